@@ -1,0 +1,108 @@
+"""ctypes binding of ``libactnn_b200.so`` (the C ABI declared in ``include/actnn_b200.h``).
+
+This is the only place that touches the shared library.  There is no fallback of any
+kind: if the library is missing or a call returns a non-zero status, a ``RuntimeError``
+is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_uint64, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libactnn_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+_DTYPE_ID = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+_P, _I, _L, _U, _F, _D = c_void_p, c_int, c_int64, c_uint64, c_float, c_double
+
+# name -> argument types, exactly as declared in include/actnn_b200.h
+SIGNATURES = {
+    "actnn_minimax": [_P, _P, _P, _L, _L, _I, _P],
+    "actnn_bits_prefix": [_P, _L, _L, _L, _P, _P],
+    "actnn_pack_mixed": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _P, _U, _U, _P],
+    "actnn_unpack_mixed": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _P],
+    "actnn_pack_single": [_P, _P, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I, _I, _P, _U, _U, _P],
+    "actnn_unpack_single": [_P, _I, _P, _P, _P, _L, _L, _L, _I, _I, _P],
+    "actnn_compress_single": [_P, _I, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _P, _U, _U, _P],
+    "actnn_range_sqr": [_P, _P, _L, _L, _I, _F, _F, _P, _P, _P],
+    "actnn_calc_precision": [_P, _P, _L, _I, _D, _P, _P, _L, _L, _P],
+    "actnn_relu_forward": [_P, _P, _P, _L, _I, _P],
+    "actnn_relu_backward": [_P, _P, _P, _L, _I, _P],
+    "actnn_dropout_forward": [_P, _P, _P, _L, _F, _I, _P, _U, _U, _P],
+    "actnn_dropout_backward": [_P, _P, _P, _L, _F, _I, _P],
+    "actnn_dropout_uniform_fill": [_P, _L, _U, _U, _P],
+    "actnn_max_pool2d_forward": [_P, _P, _P, _L, _L, _L, _L] + [_I] * 9 + [_P],
+    "actnn_max_pool2d_backward": [_P, _P, _P, _L, _L, _L, _L] + [_I] * 9 + [_P],
+    "actnn_noise_fill": [_P, _L, _I, _U, _U, _P],
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once; fail loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "actnn_b200: %s is missing. Build it with `python -m actnn_b200.csrc.build` "
+                "(nvcc, sm_100a). There is no CPU or PyTorch fallback." % LIB_PATH)
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        lib.actnn_status_string.argtypes = [c_int]
+        lib.actnn_status_string.restype = c_char_p
+        lib.actnn_abi_version.argtypes = []
+        lib.actnn_abi_version.restype = c_int
+        _lib = lib
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = load().actnn_status_string(status).decode()
+        raise RuntimeError("%s failed: %s (status %d)" % (what, msg, status))
+
+
+def dtype_id(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_ID[dtype]
+    except KeyError:
+        raise RuntimeError("actnn_b200: unsupported dtype %s" % dtype) from None
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def stream_of(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def call(name: str, tensor_for_device: torch.Tensor, *args) -> None:
+    """Invoke ``name`` with the tensor's device current and check the status."""
+    lib = load()
+    dev = tensor_for_device.device
+    if dev.index is not None and dev.index != torch.cuda.current_device():
+        with torch.cuda.device(dev):
+            check(getattr(lib, name)(*args), name)
+    else:
+        check(getattr(lib, name)(*args), name)
+
+
+def next_philox(device: torch.device):
+    """(seed, offset) from torch's default CUDA generator of ``device``; advances the offset
+    so that ``torch.manual_seed`` reproduces a whole run, as the reference does with
+    ``philox_engine_inputs`` (quantization_cuda_kernel.cu:115-121)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    gen = torch.cuda.default_generators[idx]
+    seed, offset = gen.initial_seed(), gen.get_offset()
+    gen.set_offset(offset + 4)
+    return seed & 0xFFFFFFFFFFFFFFFF, offset

@@ -1,0 +1,79 @@
+// Status strings, cached device properties, launch checking and the noise export.
+#include "quant_math.cuh"
+
+namespace actnn {
+
+const DeviceInfo& device_info() {
+  // Immutable per-device facts, filled on first use.  Racing first calls write the same
+  // values, so no lock is needed.
+  static DeviceInfo info[64];
+  static bool ready[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!ready[dev]) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    info[dev].sm_count = sms;
+    ready[dev] = true;
+  }
+  return info[dev];
+}
+
+int check_launch() { return cudaPeekAtLastError() == cudaSuccess ? ACTNN_OK : ACTNN_ERR_LAUNCH; }
+
+namespace {
+
+// One thread per octet of the padded [N, G, 256] activation.
+template <typename T>
+__global__ void noise_fill_kernel(T* __restrict__ out, int64_t numel, NoiseKey key) {
+  const int64_t oct = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (oct * kOct >= numel) return;
+  const uint64_t q = (uint64_t)(oct >> 5);        // 32 octets per 256-element group
+  NoiseGen<T> gen(key, (int)(oct & 31));
+  const Oct<T> nz = gen.get(q);
+  const T* e = reinterpret_cast<const T*>(&nz);
+  for (int j = 0; j < kOct && oct * kOct + j < numel; ++j) out[oct * kOct + j] = e[j];
+}
+
+}  // namespace
+}  // namespace actnn
+
+using namespace actnn;
+
+extern "C" const char* actnn_status_string(int status) {
+  switch (status) {
+    case ACTNN_OK: return "ok";
+    case ACTNN_ERR_NULL: return "a required pointer is NULL";
+    case ACTNN_ERR_DTYPE: return "unsupported dtype (float32, float16 and bfloat16 are accepted; statistics must "
+                                 "match the data dtype, or be bfloat16 for float32 data)";
+    case ACTNN_ERR_SHAPE: return "invalid shape (negative size, overflow, or a group size other than 256; minimax "
+                                 "needs cols % 32 == 0 and cols > 32)";
+    case ACTNN_ERR_BITS: return "unsupported bit width (single precision: 1, 2, 4, 8; mixed precision: 1..8)";
+    case ACTNN_ERR_ALIGN: return "pointer not aligned for vector access (16 bytes; 32 for float32 data)";
+    case ACTNN_ERR_ARG: return "invalid argument";
+    case ACTNN_ERR_LAUNCH: return "CUDA launch failed";
+    case ACTNN_ERR_CAPACITY: return "problem exceeds a fixed internal capacity";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int actnn_abi_version(void) { return 1; }
+
+extern "C" int actnn_noise_fill(void* noise, int64_t numel, int dtype, uint64_t seed, uint64_t offset,
+                                actnn_stream_t stream) {
+  if (numel < 0) return ACTNN_ERR_SHAPE;
+  if (numel == 0) return ACTNN_OK;
+  if (!noise) return ACTNN_ERR_NULL;
+  const int64_t octs = (numel + kOct - 1) / kOct;
+  const unsigned grid = (unsigned)((octs + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  const NoiseKey key = make_noise_key(seed, offset);
+  switch (dtype) {
+    case ACTNN_F32: noise_fill_kernel<float><<<grid, 256, 0, s>>>((float*)noise, numel, key); break;
+    case ACTNN_F16: noise_fill_kernel<__half><<<grid, 256, 0, s>>>((__half*)noise, numel, key); break;
+    case ACTNN_BF16: noise_fill_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)noise, numel, key); break;
+    default: return ACTNN_ERR_DTYPE;
+  }
+  return check_launch();
+}

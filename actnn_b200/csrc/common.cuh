@@ -1,0 +1,174 @@
+// Shared device helpers for the actnn_b200 kernels (sm_100a only).
+//
+// Everything on this path is a streaming codec bound by HBM bandwidth, so the helpers are
+// about moving bytes well: 128/256-bit global loads and stores, one-instruction warp
+// min/max (redux.sync.f32, new with sm_100a), a 32x32 bit-matrix transpose across the
+// lanes of a warp (the packed layouts are "lane ballots", see quant_math.cuh), and a
+// counter-based Philox generator that lives entirely in registers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/actnn_b200.h"
+
+#define ACTNN_HD __host__ __device__ __forceinline__
+#define ACTNN_DEV __device__ __forceinline__
+
+namespace actnn {
+
+constexpr int kGroup = 256;          // elements per quantization group on the fast paths
+constexpr int kOct = 8;              // consecutive elements one lane owns inside a group
+constexpr unsigned kFull = 0xffffffffu;
+
+// ------------------------------------------------------------------ dtype plumbing
+template <typename T> struct DType;
+template <> struct DType<float> { static constexpr int id = ACTNN_F32; };
+template <> struct DType<__half> { static constexpr int id = ACTNN_F16; };
+template <> struct DType<__nv_bfloat16> { static constexpr int id = ACTNN_BF16; };
+
+static inline int dtype_size(int dtype) { return dtype == ACTNN_F32 ? 4 : 2; }
+
+// Eight consecutive elements of T, as they sit in registers after one vector load.
+template <typename T> struct Oct { uint32_t r[4]; };          // 16-bit types: 4 x (lo, hi)
+template <> struct Oct<float> { float f[8]; };
+
+#ifdef __CUDACC__
+// ------------------------------------------------------------------ vector memory ops
+// Streaming loads bypass L1 allocation: every byte of the activation is touched once.
+template <typename T> ACTNN_DEV Oct<T> load_oct(const T* p) {
+  Oct<T> o;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(o.r[0]), "=r"(o.r[1]), "=r"(o.r[2]), "=r"(o.r[3]) : "l"(p));
+  return o;
+}
+template <> ACTNN_DEV Oct<float> load_oct<float>(const float* p) {
+  Oct<float> o;     // one 256-bit load (sm_100): 32 lanes x 32 B = 1 KiB contiguous per warp
+  asm volatile("ld.global.nc.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(o.f[0]), "=f"(o.f[1]), "=f"(o.f[2]), "=f"(o.f[3]),
+                 "=f"(o.f[4]), "=f"(o.f[5]), "=f"(o.f[6]), "=f"(o.f[7]) : "l"(p));
+  return o;
+}
+template <typename T> ACTNN_DEV void store_oct(T* p, const Oct<T>& o) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};"
+               :: "l"(p), "r"(o.r[0]), "r"(o.r[1]), "r"(o.r[2]), "r"(o.r[3]) : "memory");
+}
+template <> ACTNN_DEV void store_oct<float>(float* p, const Oct<float>& o) {
+  asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               :: "l"(p), "f"(o.f[0]), "f"(o.f[1]), "f"(o.f[2]), "f"(o.f[3]),
+                  "f"(o.f[4]), "f"(o.f[5]), "f"(o.f[6]), "f"(o.f[7]) : "memory");
+}
+template <typename T> ACTNN_DEV Oct<T> zero_oct() {
+  Oct<T> o;
+  for (int i = 0; i < 4; ++i) o.r[i] = 0u;
+  return o;
+}
+template <> ACTNN_DEV Oct<float> zero_oct<float>() {
+  Oct<float> o;
+  for (int i = 0; i < 8; ++i) o.f[i] = 0.f;
+  return o;
+}
+
+// ------------------------------------------------------------------ warp reductions
+ACTNN_DEV float warp_min(float v) {
+  float r;
+  asm volatile("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+ACTNN_DEV float warp_max(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// ------------------------------------------------------------------ 32x32 bit transpose
+// Lane r holds row r of a 32x32 bit matrix (bit c = column c).  Afterwards lane r holds
+// column r of the original (bit c = original lane c, bit r).  Five butterfly stages; per
+// stage one shuffle, one funnel shift (a rotate) and one LOP3 bit-select.
+struct TransposePlan {
+  uint32_t keep[5];   // bits this lane keeps at stage s = 16, 8, 4, 2, 1
+  uint32_t rot[5];    // left-rotate applied to the partner's word
+};
+ACTNN_DEV TransposePlan make_transpose_plan(int lane) {
+  TransposePlan p;
+  const uint32_t m[5] = {0x0000ffffu, 0x00ff00ffu, 0x0f0f0f0fu, 0x33333333u, 0x55555555u};
+#pragma unroll
+  for (int k = 0; k < 5; ++k) {
+    const int s = 16 >> k;
+    const bool low = (lane & s) == 0;
+    p.keep[k] = low ? m[k] : ~m[k];
+    p.rot[k] = low ? s : 32 - s;
+  }
+  return p;
+}
+ACTNN_DEV uint32_t warp_transpose32(uint32_t x, const TransposePlan& p) {
+#pragma unroll
+  for (int k = 0; k < 5; ++k) {
+    const uint32_t y = __shfl_xor_sync(kFull, x, 16 >> k);
+    const uint32_t ry = __funnelshift_l(y, y, p.rot[k]);
+    x = (x & p.keep[k]) | (ry & ~p.keep[k]);
+  }
+  return x;
+}
+#endif  // __CUDACC__
+
+// ------------------------------------------------------------------ Philox4x32-10
+// Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3" (SC'11).
+struct Philox4 { uint32_t v[4]; };
+
+ACTNN_HD void philox_mulhilo(uint32_t a, uint32_t b, uint32_t& hi, uint32_t& lo) {
+  const uint64_t p = (uint64_t)a * (uint64_t)b;
+  hi = (uint32_t)(p >> 32);
+  lo = (uint32_t)p;
+}
+ACTNN_HD Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                               uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    uint32_t hi0, lo0, hi1, lo1;
+    philox_mulhilo(0xD2511F53u, c0, hi0, lo0);
+    philox_mulhilo(0xCD9E8D57u, c2, hi1, lo1);
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  Philox4 o;
+  o.v[0] = c0; o.v[1] = c1; o.v[2] = c2; o.v[3] = c3;
+  return o;
+}
+
+// Rounding-noise stream, indexed by position in the padded [N, G, 256] activation:
+// flat group q, position d in the group, lane t = d / 8, j = d % 8.
+//   counter = (lo32(c), hi32(c), lo32(offset), hi32(offset)), key = (lo32(seed), hi32(seed))
+//   16-bit activations: c = (q >> 1) * 32 + t; byte f = (q & 1) * 8 + j of the 128-bit
+//     output (little endian over v[0..3]) is k in [0, 255]; noise = (2k + 1 - 256) / 512.
+//     One call serves one lane for two neighbouring groups.
+//   float32 activations: c = q * 32 + t; 16-bit field j (v[j / 2] >> 16 * (j % 2)) is k;
+//     noise = (2k + 1 - 65536) / 131072.
+// Both are odd multiples of the step, symmetric about zero, strictly inside (-0.5, 0.5)
+// and exactly representable in the activation dtype.  The resolution follows the dtype:
+// (x - min) * scale carries at most 11 (float16) or 8 (bfloat16) significant bits.
+struct NoiseKey { uint32_t k0, k1, o0, o1; };
+ACTNN_HD NoiseKey make_noise_key(uint64_t seed, uint64_t offset) {
+  NoiseKey k;
+  k.k0 = (uint32_t)seed; k.k1 = (uint32_t)(seed >> 32);
+  k.o0 = (uint32_t)offset; k.o1 = (uint32_t)(offset >> 32);
+  return k;
+}
+ACTNN_HD Philox4 noise_call(const NoiseKey& key, uint64_t c) {
+  return philox4x32_10((uint32_t)c, (uint32_t)(c >> 32), key.o0, key.o1, key.k0, key.k1);
+}
+
+// ------------------------------------------------------------------ host-side launch helpers
+struct DeviceInfo { int sm_count; };
+const DeviceInfo& device_info();                   // api.cu (per current device, cached)
+int check_launch();                                // api.cu: cudaPeekAtLastError -> status
+
+static inline bool aligned(const void* p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+}  // namespace actnn

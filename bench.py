@@ -1,0 +1,396 @@
+"""Benchmark of the activation compress / decompress hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+One STEP = one pass of the codec over one batch of synthetic activations of the headline
+workload: a float16 activation of shape [256, 256, 28, 28] (51.4 M elements, 256-element
+groups), compressed to 2 bits with the fused single-pass kernel (min/max + stochastic
+rounding + pack) and decompressed again.  Metric: algorithmic GB/s of compress +
+decompress, i.e. per element  s + b/8 + 2*s_stat/gs  bytes each way (s = 2 bytes, b = 2
+bits, two 2-byte statistics per 256-element group) = 232.8 MB per step.
+
+The printed JSON line carries
+  value       device-resident throughput (inputs in HBM, raw C-ABI calls, CUDA-event timed);
+  e2e         the same work through the public Python API from pinned HOST buffers:
+              H2D copy -> quantize_activation -> dequantize_activation -> D2H copy;
+  roofline    the dominant kernel (fused compress) against the measured HBM copy peak;
+  kernels     per-kernel GB/s for the other kernels of the path (informational);
+  cpu_baseline  the CPU oracle (a restatement of the reference's simulate path) timed on the
+              host cores over a bounded sample of the same workload (rank 0, N = 1 only).
+`--impl reference` times only that CPU implementation and prints the reference arm's line.
+
+Inputs rotate through a pool whose total size is several times the 126 MB L2, and a packed
+buffer is decoded only after half the pool has been re-written, so neither the activation
+reads nor the packed reads are served from L2.
+With N > 1 every rank processes its own batch on its own GPU (the codec is independent per
+sample: no data-path collective); value = all ranks' bytes / max-over-ranks time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = {"name": "cfg2-activation-codec", "shape": [256, 256, 28, 28], "dtype": "float16", "bits": 2,
+            "group_size": 256}
+POOL = 8                                    # rotating buffers: 8 x 102.8 MB in, 8 x 13.6 MB packed
+
+
+def algorithmic_bytes(elements: int, elem_size: int, bits: float, stat_size: int = 2, gs: int = 256) -> float:
+    """Bytes one direction of the codec must move: the activation, the packed codes and the
+    two per-group statistics."""
+    return elements * (elem_size + bits / 8.0 + 2.0 * stat_size / gs)
+
+
+# ---------------------------------------------------------------------------------------
+# clocks: sampled with NVML from a side thread while the GPU is under load
+# ---------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if visible:
+                index = int(visible.split(",")[index]) if visible.split(",")[index].isdigit() else index
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _run(self):
+        n = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+                mask = n.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nvml:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "window": "unavailable"}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s), "window": "pre-heat + timed region"}
+
+
+# ---------------------------------------------------------------------------------------
+# the CPU arm: the oracle (restated reference simulate path) on the host cores
+# ---------------------------------------------------------------------------------------
+def cpu_round_trip_gbs(sample_n: int, repeats: int, warmup: int = 1):
+    """GB/s of compress + decompress of the first `sample_n` samples of the workload with the
+    CPU oracle, all host threads.  Returns (gbs, seconds_per_pass, cores)."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import actnn_oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    _, c, h, w = WORKLOAD["shape"]
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(sample_n, c, h, w, generator=g).to(torch.float16)
+    shape = tuple(x.shape)
+
+    def one_pass():
+        q = O.quantize_activation(x, WORKLOAD["bits"], lambda gr: O.torch_noise(gr.shape, gr.dtype, g), scheme=False)
+        return O.dequantize_activation(q, shape, dtype=x.dtype)
+
+    for _ in range(warmup):
+        one_pass()
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    nbytes = 2 * algorithmic_bytes(x.numel(), 2, WORKLOAD["bits"])
+    return nbytes / sec / 1e9, sec, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_n = 16
+    warm = max(args.warmup, 1)
+    import torch  # noqa: F401
+    gbs, sec, cores = cpu_round_trip_gbs(sample_n, args.steps, warmup=min(warm, 3))
+    line = {
+        "impl": "reference", "metric": "pack+unpack HBM GB/s", "value": round(gbs, 4), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "shape": WORKLOAD["shape"], "bits": WORKLOAD["bits"],
+                   "group_size": 256, "step": "compress + decompress of %d of the 256 samples" % sample_n},
+        "cpu_baseline": {"value": round(gbs, 4), "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "%d of 256 samples of the cfg2 activation per step; the reference's simulate "
+                                   "path restated for CPU tensors (oracle/actnn_oracle.py), torch threads = cores"
+                                   % sample_n},
+        "e2e": {"value": round(gbs, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import actnn_b200 as actnn
+    from actnn_b200 import _lib
+    from actnn_b200.cpp_extension import minimax, quantization
+    from actnn_b200.cpp_extension import calc_precision
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    N, C, H, W = WORKLOAD["shape"]
+    bits, gs = WORKLOAD["bits"], 256
+    elements = N * C * H * W
+    G = C * H * W // gs
+    dt = torch.float16
+    F16 = _lib.dtype_id(dt)
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    one_way = algorithmic_bytes(elements, 2, bits)
+    step_bytes = 2 * one_way
+
+    torch.manual_seed(1234 + rank)
+    xs = [torch.randn(N, G, gs, device=dev, dtype=dt) for _ in range(POOL)]
+    packed = [torch.empty(quantization.single_precision_bytes(bits, N, G, gs), dtype=torch.int8, device=dev)
+              for _ in range(POOL)]
+    scales = [torch.empty(N, G, 1, dtype=dt, device=dev) for _ in range(POOL)]
+    mins = [torch.empty(N, G, 1, dtype=dt, device=dev) for _ in range(POOL)]
+    outs = [torch.empty(N, G, gs, dtype=dt, device=dev) for _ in range(2)]
+
+    def compress(i, step_no):
+        _lib.check(lib.actnn_compress_single(xs[i].data_ptr(), bits, packed[i].data_ptr(), scales[i].data_ptr(),
+                                             mins[i].data_ptr(), None, N, G, gs, F16, F16, 1, None, 1234 + rank,
+                                             4 * step_no, stream), "actnn_compress_single")
+
+    def decompress(i, o):
+        _lib.check(lib.actnn_unpack_single(packed[i].data_ptr(), bits, scales[i].data_ptr(), mins[i].data_ptr(),
+                                           outs[o].data_ptr(), N, G, gs, F16, F16, stream), "actnn_unpack_single")
+
+    def step(k):
+        compress(k % POOL, k)
+        decompress((k + POOL // 2) % POOL, k % 2)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    with sampler:
+        for i in range(POOL):                               # fill the pool so every decode has input
+            compress(i, i)
+        for k in range(max(args.warmup, 3)):
+            step(k)
+        # pre-heat ~0.2 s so that the clocks seen are clocks under load
+        t_end = time.perf_counter() + 0.2
+        k = 0
+        while time.perf_counter() < t_end:
+            for _ in range(50):
+                step(k)
+                k += 1
+            torch.cuda.synchronize()
+
+        # ---- timed region: exactly K steps, CUDA events on the launching stream
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+        barrier()
+        ev[0].record()
+        for k in range(args.steps):
+            compress(k % POOL, k)
+            ev[2 * k + 1].record()
+            decompress((k + POOL // 2) % POOL, k % 2)
+            ev[2 * k + 2].record()
+        barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    pack_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps)) / args.steps
+    unpack_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(args.steps)) / args.steps
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- other kernels of the path, each timed alone over the rotating pool (informational)
+    def time_kernel(fn, reps=16):
+        for r in range(3):
+            fn(r)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for r in range(reps):
+            fn(r)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    kernels = {}
+    if rank == 0:
+        stat_b = 2.0 * 2 / gs
+        kernels["compress_single_2b_fused"] = {"ms": round(pack_ms, 5), "gbs": round(one_way / pack_ms / 1e6, 1)}
+        kernels["unpack_single_2b"] = {"ms": round(unpack_ms, 5), "gbs": round(one_way / unpack_ms / 1e6, 1)}
+        mn = [torch.empty(N * G, dtype=dt, device=dev) for _ in range(2)]
+        ms = time_kernel(lambda r: lib.actnn_minimax(xs[r % POOL].data_ptr(), mn[0].data_ptr(), mn[1].data_ptr(),
+                                                    N * G, gs, F16, stream))
+        kernels["minimax"] = {"ms": round(ms, 5), "gbs": round(elements * (2 + stat_b) / ms / 1e6, 1)}
+        # adaptive (L3) path: 2.0-bit average, per-sample widths from LogNormal sensitivities
+        Cs = torch.exp(torch.randn(N, device=dev))
+        bt, offs = calc_precision.allocate_bits(Cs, 8, 2 * N, None, G, gs, with_offsets=True)
+        words = 2 * N * G * gs // 32
+        pm = [torch.empty(words, dtype=torch.int32, device=dev) for _ in range(POOL)]
+        mnx = []
+        for i in range(POOL):
+            a, b = minimax.minimax(xs[i].view(-1, gs))
+            mnx.append((a, b))
+        ms = time_kernel(lambda r: lib.actnn_pack_mixed(
+            xs[r % POOL].data_ptr(), mnx[r % POOL][0].data_ptr(), mnx[r % POOL][1].data_ptr(), bt.data_ptr(),
+            offs.data_ptr(), pm[r % POOL].data_ptr(), scales[r % POOL].data_ptr(), None, N, G, gs, F16, F16, 1,
+            None, 7, 4 * r, stream))
+        kernels["pack_mixed_2b_avg"] = {"ms": round(ms, 5), "gbs": round((one_way + elements * stat_b) / ms / 1e6, 1)}
+        ms = time_kernel(lambda r: lib.actnn_unpack_mixed(
+            pm[(r + 4) % POOL].data_ptr(), bt.data_ptr(), offs.data_ptr(), scales[(r + 4) % POOL].data_ptr(),
+            mnx[(r + 4) % POOL][0].data_ptr(), outs[r % 2].data_ptr(), N, G, gs, F16, F16, stream))
+        kernels["unpack_mixed_2b_avg"] = {"ms": round(ms, 5), "gbs": round(one_way / ms / 1e6, 1)}
+        ms = time_kernel(lambda r: lib.actnn_calc_precision(Cs.data_ptr(), None, N, 8, float(2 * N), bt.data_ptr(),
+                                                           offs.data_ptr(), G, gs, stream))
+        kernels["calc_precision_n256"] = {"ms": round(ms, 5)}
+        del pm, mnx
+        masks = [torch.empty((elements + 31) // 32, dtype=torch.int32, device=dev) for _ in range(POOL)]
+        ms = time_kernel(lambda r: lib.actnn_relu_forward(xs[r % POOL].data_ptr(), outs[r % 2].data_ptr(),
+                                                         masks[r % POOL].data_ptr(), elements, F16, stream))
+        kernels["relu_forward"] = {"ms": round(ms, 5), "gbs": round(elements * (4 + 1 / 8) / ms / 1e6, 1)}
+        ms = time_kernel(lambda r: lib.actnn_relu_backward(xs[r % POOL].data_ptr(), masks[(r + 4) % POOL].data_ptr(),
+                                                          outs[r % 2].data_ptr(), elements, F16, stream))
+        kernels["relu_backward"] = {"ms": round(ms, 5), "gbs": round(elements * (4 + 1 / 8) / ms / 1e6, 1)}
+        del masks
+
+    # ---- end to end through the public API, host buffers in, host buffers out
+    actnn.set_optimization_level("L2")                      # uniform width, no adaptive scheme
+    actnn.config.activation_compression_bits = [bits]
+    shape = (N, C, H, W)
+    host_in = [torch.randn(shape, dtype=dt).pin_memory() for _ in range(2)]
+    host_out = [torch.empty(shape, dtype=dt).pin_memory() for _ in range(2)]
+    dev_in = torch.empty(shape, dtype=dt, device=dev)
+
+    def e2e_step(k):
+        dev_in.copy_(host_in[k % 2], non_blocking=True)
+        q = actnn.ops.quantize_activation(dev_in, None)
+        y = actnn.ops.dequantize_activation(q, shape, dt)
+        host_out[k % 2].copy_(y, non_blocking=True)
+
+    for k in range(3):
+        e2e_step(k)
+    e2e_steps = max(3, min(args.steps, 20))
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for k in range(e2e_steps):
+        e2e_step(k)
+    b.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json, copy kernel)"
+        else:
+            peak, peak_src = 6650.0, "fallback (earlier measurement on this pool)"
+        achieved = one_way / (pack_ms * 1e-3) / 1e9
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+        if os.path.exists(tpath):
+            traffic = json.load(open(tpath)).get("compress_single_2b_fused_bytes_per_launch")
+        line = {
+            "metric": "pack+unpack HBM GB/s", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD["name"], "shape": WORKLOAD["shape"], "bits": bits, "group_size": gs,
+                       "step": "fused 2-bit compress + decompress of one [256,256,28,28] float16 activation",
+                       "bytes_per_step": step_bytes, "l2": "inputs rotate over a pool of %d buffers (%.0f MB), "
+                       "larger than L2; packed buffers are decoded %d steps after they were written"
+                       % (POOL, POOL * elements * 2 / 1e6, POOL // 2), "parallelism": "replicas x%d" % world},
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": elements * 2,
+                    "d2h_bytes_per_step": elements * 2, "ms_per_step": round(e2e_ms, 4),
+                    "path": "pinned host -> H2D -> ops.quantize_activation -> ops.dequantize_activation -> D2H"},
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"kernel": "pack_single_kernel<half, 2 bit, fused> (actnn_compress_single)", "bound": "hbm",
+                         "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": one_way},
+            "kernels": kernels,
+            "clocks": sampler.summary(),
+        }
+        if world == 1:
+            gbs, sec, cores = cpu_round_trip_gbs(16, repeats=5)
+            line["cpu_baseline"] = {"value": round(gbs, 4), "unit": "GB/s", "cores": cores, "kind": "port",
+                                    "sample": "16 of the 256 samples, 5 passes (%.2f s each), CPU oracle = the "
+                                              "reference's simulate path restated for CPU tensors" % sec}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

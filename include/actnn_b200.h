@@ -1,0 +1,211 @@
+/*
+ * actnn_b200 -- C ABI of the B200 (sm_100a) activation compress / decompress kernels.
+ *
+ * Drop-in boundary for the native extensions of ucbrise/actnn
+ * (actnn/actnn/cpp_extension/{minimax,quantization,calc_precision}*).  The reference
+ * binds those as pybind11 torch extensions that take and return torch::Tensor; this
+ * library exposes the same operations one level lower: plain device pointers, explicit
+ * sizes, a dtype tag and a cudaStream_t.  A binding layer (python/ctypes here, or the
+ * reference's own .cc files) allocates the outputs and forwards the pointers.
+ *
+ * Conventions
+ *   - every pointer is a device pointer on the current device unless stated otherwise;
+ *   - no entry point allocates, frees or synchronises; all work is queued on `stream`;
+ *   - every entry point returns an actnn_status (0 = queued successfully); arguments are
+ *     validated on the host before anything is launched;
+ *   - activations are viewed as [N, G, group_size] (sample, group, element), contiguous,
+ *     each sample zero-padded to a whole number of groups by the caller, as the
+ *     reference's schemes do (actnn/actnn/qscheme.py:61-71);
+ *   - `dtype` is the element type of the activation; per-group statistics (min, max,
+ *     scale) carry `stat_dtype`, which equals `dtype` except that float32 activations may
+ *     keep bfloat16 statistics (the reference's storage format, actnn/actnn/ops.py:115-116);
+ *   - the arithmetic is the reference's "simulate" branch (actnn/actnn/ops.py:23-41,56-57)
+ *     with every intermediate rounded to `dtype`, so codes and packed bytes are bit-exact
+ *     against it for the same rounding noise;
+ *   - rounding noise: pass `noise` (device array, same shape and dtype as the activation,
+ *     values in [-0.5, 0.5]) to inject it, or NULL to draw it in registers from
+ *     Philox4x32-10 keyed by (seed, offset); actnn_noise_fill() materialises exactly that
+ *     stream.  `stochastic == 0` rounds to nearest without noise.
+ *   - a NaN input is encoded as code 0.
+ */
+#ifndef ACTNN_B200_H_
+#define ACTNN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* actnn_stream_t;        /* == cudaStream_t */
+
+typedef enum {
+  ACTNN_F32 = 0,
+  ACTNN_F16 = 1,
+  ACTNN_BF16 = 2
+} actnn_dtype;
+
+typedef enum {
+  ACTNN_OK = 0,
+  ACTNN_ERR_NULL = 1,         /* a required pointer is NULL */
+  ACTNN_ERR_DTYPE = 2,        /* dtype / stat_dtype not supported by this entry point */
+  ACTNN_ERR_SHAPE = 3,        /* negative size, size overflow, unsupported group size */
+  ACTNN_ERR_BITS = 4,         /* bit width outside the supported set */
+  ACTNN_ERR_ALIGN = 5,        /* pointer not aligned for vector access */
+  ACTNN_ERR_ARG = 6,          /* any other invalid argument (e.g. stochastic rounding off where the reference requires it) */
+  ACTNN_ERR_LAUNCH = 7,       /* the CUDA runtime refused the launch; see cudaGetLastError() */
+  ACTNN_ERR_CAPACITY = 8      /* problem larger than a fixed internal buffer */
+} actnn_status;
+
+/* Human-readable text for a status code (static storage). */
+const char* actnn_status_string(int status);
+/* Library ABI version, bumped on any signature change. */
+int actnn_abi_version(void);
+
+/* ------------------------------------------------------------------------------------
+ * Per-group min / max.
+ * Replaces: minimax(data) -> (min, max), actnn/actnn/cpp_extension/minimax.cc:7-11 and
+ * minimax_cuda_kernel.cu:23-89.  data[rows, cols] -> mn[rows], mx[rows], all `dtype`.
+ * The reference requires cols % 32 == 0 && cols > 32; so does this.  cols == 256 takes
+ * the vectorised path (one warp per row, 128/256-bit loads).
+ */
+int actnn_minimax(const void* data, void* mn, void* mx, int64_t rows, int64_t cols,
+                  int dtype, actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Mixed-precision bit stream (per-sample bit widths, int32 words).
+ * Layout (actnn/actnn/cpp_extension/quantization_cuda_kernel.cu:51-79): the block of
+ * (sample n, group g) starts at word (P[n-1]*G*gs + bits[n]*g*gs) / 32, P the inclusive
+ * prefix sum of bits; bit i of element d sits in word (d*b+i) % W at bit (d*b+i) / W,
+ * W = gs*b/32.
+ *
+ * actnn_bits_prefix: word_offsets[n] = first word of sample n, word_offsets[N] = total
+ * words.  Replaces the torch::cumsum + .item() of quantization_cuda_kernel.cu:97-98 /
+ * :182 without a host sync.  One thread block; N <= 2^20.
+ */
+int actnn_bits_prefix(const int32_t* bits, int64_t N, int64_t G, int64_t group_size,
+                      int64_t* word_offsets, actnn_stream_t stream);
+
+/* Replaces: pack_mixed_precision(data, min, max, bits, stochastic) -> (packed, scale),
+ * actnn/actnn/cpp_extension/quantization.cc:46-57, quantization_cuda_kernel.cu:37-142.
+ * data[N,G,gs], mn/mx[N,G] in `dtype`; bits[N] in 1..8; word_offsets from
+ * actnn_bits_prefix; writes packed (word_offsets[N] words) and scale[N,G] (`stat_dtype`).
+ * If mn_out is not NULL the minimum is also re-written there in `stat_dtype`.
+ * group_size must be 256. */
+int actnn_pack_mixed(const void* data, const void* mn, const void* mx, const int32_t* bits,
+                     const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out,
+                     int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype,
+                     int stochastic, const void* noise, uint64_t seed, uint64_t offset,
+                     actnn_stream_t stream);
+
+/* Replaces: unpack_mixed_precision(data, bits, scale, min, N, num_groups, group_size),
+ * actnn/actnn/cpp_extension/quantization.cc:59-73, quantization_cuda_kernel.cu:145-205.
+ * out[N,G,gs] in `dtype` = code / scale + min. */
+int actnn_unpack_mixed(const int32_t* packed, const int32_t* bits, const int64_t* word_offsets,
+                       const void* scale, const void* mn, void* out,
+                       int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype,
+                       actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Single-precision (uniform bit width) byte stream, int8.
+ * Layout (quantization_cuda_kernel.cu:236-257): byte (no*G + g)*gs + d holds samples
+ * no*wpt + ni (wpt = 8 / bits) at bit offset ni*bits; length
+ * bits * N_round * G * gs / 8 + 1 with N rounded up to a multiple of wpt (the trailing
+ * byte is written as zero).  bits in {1, 2, 4, 8}; group_size must be 256.
+ *
+ * Replaces: pack_single_precision(data, min, max, bits, stochastic) -> (packed, scale),
+ * actnn/actnn/cpp_extension/quantization.cc:77-87, quantization_cuda_kernel.cu:225-330. */
+int actnn_pack_single(const void* data, const void* mn, const void* mx, int bits,
+                      int8_t* packed, void* scale, void* mn_out,
+                      int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype,
+                      int stochastic, const void* noise, uint64_t seed, uint64_t offset,
+                      actnn_stream_t stream);
+
+/* Replaces: unpack_single_precision(data, bits, scale, min, N, num_groups, group_size),
+ * actnn/actnn/cpp_extension/quantization.cc:89-102, quantization_cuda_kernel.cu:333-405. */
+int actnn_unpack_single(const int8_t* packed, int bits, const void* scale, const void* mn,
+                        void* out, int64_t N, int64_t G, int64_t group_size, int dtype,
+                        int stat_dtype, actnn_stream_t stream);
+
+/* Fused single pass: per-group min/max + stochastic rounding + pack, reading the
+ * activation once.  Replaces the sequence minimax -> pack_single_precision that
+ * no_scheme_compute_quantization_bits + quantize_and_pack issue for uniform-bit layers
+ * (actnn/actnn/ops.py:77-96, 44-48).  Writes packed, scale[N,G] and mn[N,G]
+ * (`stat_dtype`); mx_out may be NULL. */
+int actnn_compress_single(const void* data, int bits, int8_t* packed, void* scale, void* mn_out,
+                          void* mx_out, int64_t N, int64_t G, int64_t group_size, int dtype,
+                          int stat_dtype, int stochastic, const void* noise, uint64_t seed,
+                          uint64_t offset, actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Bit allocation on the device.
+ *
+ * actnn_range_sqr: per-sample sensitivity base, Range_sqr[n] =
+ * float(norm_T(mx[n,:] - mn[n,:]))^2 * (group_size / num_pixels), the expression of
+ * actnn/actnn/qscheme.py:80 / qbnscheme.py:42; then C[n] = coeff * Range_sqr[n] *
+ * (grad_scale ? *grad_scale : 1) in float32 (qscheme.py:84).  grad_scale is a device
+ * pointer to one float or NULL. */
+int actnn_range_sqr(const void* mn, const void* mx, int64_t N, int64_t G, int stat_dtype,
+                    float range_factor, float coeff, const float* grad_scale, float* C,
+                    actnn_stream_t stream);
+
+/* Replaces: calc_precision(b, C, w, target) -> b,
+ * actnn/actnn/cpp_extension/calc_precision.cc:9-50 (a CPU priority queue there; here a
+ * weighted radix select over the (initial_bits-1)*N candidate decrements, identical
+ * results including tie-breaks).  C[N] float32, w[N] int32 or NULL (all ones),
+ * b_out[N] int32, every entry starting from `initial_bits` (2..15).  If word_offsets is
+ * not NULL it receives what actnn_bits_prefix would (needs G, group_size).
+ * One thread block; N <= 2^20. */
+int actnn_calc_precision(const float* C, const int32_t* w, int64_t N, int initial_bits,
+                         double target, int32_t* b_out, int64_t* word_offsets,
+                         int64_t G, int64_t group_size, actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Mask ops.  The saved mask is 1 bit per element: bit (e % 8) of byte e / 8, padded to
+ * whole int32 words (mask_words = ceil(numel / 32)).
+ *
+ * Replaces: act_quantized_relu forward / backward,
+ * actnn/actnn/cpp_extension/quantization.cc:106-124, quantization_cuda_kernel.cu:411-508. */
+int actnn_relu_forward(const void* x, void* y, int32_t* mask, int64_t numel, int dtype,
+                       actnn_stream_t stream);
+int actnn_relu_backward(const void* grad_out, const int32_t* mask, void* grad_in,
+                        int64_t numel, int dtype, actnn_stream_t stream);
+
+/* Replaces: act_quantized_dropout forward / backward,
+ * actnn/actnn/cpp_extension/quantization.cc:128-148, quantization_cuda_kernel.cu:514-627.
+ * keep = u > p with u uniform in (0, 1] from Philox (seed, offset), or from the injected
+ * float32 array `u`; y = keep ? x / (1 - p) : 0. */
+int actnn_dropout_forward(const void* x, void* y, int32_t* mask, int64_t numel, float p,
+                          int dtype, const float* u, uint64_t seed, uint64_t offset,
+                          actnn_stream_t stream);
+int actnn_dropout_backward(const void* grad_out, const int32_t* mask, void* grad_in,
+                           int64_t numel, float p, int dtype, actnn_stream_t stream);
+/* The uniforms actnn_dropout_forward draws for (seed, offset), as float32. */
+int actnn_dropout_uniform_fill(float* u, int64_t numel, uint64_t seed, uint64_t offset,
+                               actnn_stream_t stream);
+
+/* Replaces: act_quantized_max_pool2d forward / backward,
+ * actnn/actnn/cpp_extension/quantization.cc:152-196, quantization_cuda_kernel.cu:633-754.
+ * NCHW; saves the window-local arg-max kh*KW + kw as int8 per output; KH*KW < 16 as in
+ * the reference.  Backward gathers (each input sums the windows that selected it), so
+ * grad_in needs no zero fill and the result is deterministic. */
+int actnn_max_pool2d_forward(const void* x, void* y, int8_t* idx, int64_t N, int64_t C,
+                             int64_t H, int64_t W, int KH, int KW, int SH, int SW, int PH,
+                             int PW, int DH, int DW, int dtype, actnn_stream_t stream);
+int actnn_max_pool2d_backward(const void* grad_out, const int8_t* idx, void* grad_in,
+                              int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW,
+                              int SH, int SW, int PH, int PW, int DH, int DW, int dtype,
+                              actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * The rounding noise the pack kernels draw for (seed, offset) when `noise == NULL`,
+ * written as a [numel] array of `dtype` indexed like the padded [N, G, 256] activation.
+ * No counterpart in the reference (it draws cuRAND numbers it cannot replay); exists so
+ * that a CPU oracle can be fed the identical noise. */
+int actnn_noise_fill(void* noise, int64_t numel, int dtype, uint64_t seed, uint64_t offset,
+                     actnn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* ACTNN_B200_H_ */

@@ -492,21 +492,48 @@ def philox4x32_10(counter: np.ndarray, key: Tuple[int, int]) -> np.ndarray:
     return np.stack([v.astype(np.uint32) for v in c], axis=-1)
 
 
+def _philox_calls(count: int, seed: int, offset: int) -> np.ndarray:
+    """Outputs ``[count, 4]`` uint32 of calls ``c = 0..count-1`` with counter
+    ``(lo32(c), hi32(c), lo32(offset), hi32(offset))`` and key ``(lo32(seed), hi32(seed))``."""
+    c = np.arange(count, dtype=np.uint64)
+    ctr = np.stack([(c & np.uint64(0xFFFFFFFF)).astype(np.uint32), (c >> np.uint64(32)).astype(np.uint32),
+                    np.full(count, offset & 0xFFFFFFFF, dtype=np.uint32),
+                    np.full(count, (offset >> 32) & 0xFFFFFFFF, dtype=np.uint32)], axis=-1)
+    return philox4x32_10(ctr, (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
+
+
 def philox_noise(numel: int, dtype: torch.dtype, seed: int, offset: int) -> torch.Tensor:
     """The rounding noise the CUDA pack kernels draw when no noise tensor is injected.
 
-    Elements are taken eight at a time: octet ``o = e // 8`` uses counter
-    ``(lo32(o), hi32(o), lo32(offset), hi32(offset))`` and key ``(lo32(seed), hi32(seed))``;
-    element ``e`` gets the 16-bit field ``(r[j // 2] >> 16*(j % 2)) & 0xFFFF`` with
-    ``j = e % 8``; the field ``k`` becomes the float32 ``(k + 0.5) / 65536 - 0.5`` and is
-    then rounded to ``dtype``.
+    Element ``e`` of the padded ``[N, G, 256]`` activation: flat group ``q = e // 256``,
+    position ``d = e % 256``, lane ``t = d // 8``, ``j = d % 8``.
+    * float16 / bfloat16: call ``c = (q >> 1) * 32 + t``; byte ``f = (q & 1) * 8 + j`` of the
+      128-bit output (little endian over the four words) is ``k``; noise ``(2k + 1 - 256) / 512``.
+    * float32: call ``c = q * 32 + t``; 16-bit field ``j`` (word ``j // 2``, half ``j % 2``) is
+      ``k``; noise ``(2k + 1 - 65536) / 131072``.
     """
-    octets = (numel + 7) // 8
-    o = np.arange(octets, dtype=np.uint64)
-    ctr = np.stack([(o & np.uint64(0xFFFFFFFF)).astype(np.uint32), (o >> np.uint64(32)).astype(np.uint32),
-                    np.full(octets, offset & 0xFFFFFFFF, dtype=np.uint32),
-                    np.full(octets, (offset >> 32) & 0xFFFFFFFF, dtype=np.uint32)], axis=-1)
-    r = philox4x32_10(ctr, (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))          # [octets, 4]
-    fields = np.stack([r & np.uint32(0xFFFF), r >> np.uint32(16)], axis=-1).reshape(octets, 8)
-    u = (fields.astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 65536.0) - np.float32(0.5)
-    return torch.from_numpy(u.reshape(-1)[:numel].copy()).to(dtype)
+    e = np.arange(numel, dtype=np.int64)
+    q, d = e // 256, e % 256
+    t, j = d // 8, d % 8
+    if dtype == torch.float32:
+        c = q * 32 + t
+        r = _philox_calls(int(c.max()) + 1 if numel else 0, seed, offset)
+        k = (r[c, j // 2] >> (16 * (j % 2)).astype(np.uint32)) & np.uint32(0xFFFF)
+        u = (2.0 * k.astype(np.float64) + 1 - 65536) / 131072
+    else:
+        c = (q >> 1) * 32 + t
+        f = (q & 1) * 8 + j
+        r = _philox_calls(int(c.max()) + 1 if numel else 0, seed, offset)
+        k = (r[c, f // 4] >> (8 * (f % 4)).astype(np.uint32)) & np.uint32(0xFF)
+        u = (2.0 * k.astype(np.float64) + 1 - 256) / 512
+    return torch.from_numpy(u.astype(np.float32)).to(dtype)
+
+
+def philox_dropout_uniform(numel: int, seed: int, offset: int) -> torch.Tensor:
+    """The uniforms in (0, 1] the CUDA dropout draws: call ``c = e // 8``, 16-bit field
+    ``e % 8`` is ``k``, ``u = (k + 1) / 65536`` (float32)."""
+    e = np.arange(numel, dtype=np.int64)
+    c, j = e // 8, e % 8
+    r = _philox_calls(int(c.max()) + 1 if numel else 0, seed, offset)
+    k = (r[c, j // 2] >> (16 * (j % 2)).astype(np.uint32)) & np.uint32(0xFFFF)
+    return torch.from_numpy(((k.astype(np.float64) + 1) / 65536).astype(np.float32))

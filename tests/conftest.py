@@ -46,3 +46,13 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="session", autouse=True)
+def built_library():
+    """Compile ``libactnn_b200.so`` when nvcc is around (a no-op if it is up to date)."""
+    import shutil
+    from actnn_b200.csrc import build as lib_build
+    if os.path.exists(lib_build.NVCC) or shutil.which("nvcc"):
+        lib_build.build()
+    return lib_build.LIB

@@ -1,0 +1,117 @@
+"""The C ABI without a GPU: the library loads, exports everything the header declares,
+and rejects bad arguments on the host before anything would be launched."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+HEADER = os.path.join(ROOT, "include", "actnn_b200.h")
+
+
+@pytest.fixture(scope="module")
+def lib(built_library):
+    from actnn_b200 import _lib
+    return _lib.load()
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(actnn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(lib):
+    from actnn_b200 import _lib
+    names = declared_functions()
+    assert len(names) >= 18
+    for name in names:
+        assert hasattr(lib, name), "libactnn_b200.so does not export " + name
+    bound = set(_lib.SIGNATURES) | {"actnn_status_string", "actnn_abi_version"}
+    assert bound == set(names)
+
+
+def test_every_entry_point_cites_the_reference():
+    """The comment above each declaration names the reference file:line it replaces (or says
+    that the reference has no counterpart)."""
+    text = open(HEADER).read()
+    for name in declared_functions():
+        if name in ("actnn_status_string", "actnn_abi_version"):
+            continue
+        head = text[:text.index("int " + name + "(")]
+        section = head[head.rindex("/* ------"):]
+        assert re.search(r"\.(cc|cu|py):\d+", section) or "counterpart" in section, name
+
+
+def test_status_strings(lib):
+    assert lib.actnn_abi_version() >= 1
+    seen = {lib.actnn_status_string(i) for i in range(9)}
+    assert len(seen) == 9 and lib.actnn_status_string(0) == b"ok"
+
+
+def test_host_side_validation_needs_no_gpu(lib):
+    OK, NULL, DTYPE, SHAPE, BITS, ALIGN, ARG = 0, 1, 2, 3, 4, 5, 6
+    assert lib.actnn_minimax(None, None, None, 4, 30, 0, None) == SHAPE
+    assert lib.actnn_minimax(None, None, None, 4, 32, 0, None) == SHAPE          # D > 32
+    assert lib.actnn_minimax(None, None, None, 0, 256, 0, None) == OK            # empty input
+    assert lib.actnn_minimax(None, None, None, 4, 256, 0, None) == NULL
+    assert lib.actnn_minimax(16, 16, 16, 4, 256, 7, None) == DTYPE
+    assert lib.actnn_minimax(8, 16, 16, 4, 256, 1, None) == ALIGN
+    # pack / unpack
+    assert lib.actnn_pack_single(None, None, None, 3, None, None, None, 1, 1, 256, 0, 0, 1, None, 0, 0, None) == BITS
+    assert lib.actnn_pack_single(None, None, None, 2, None, None, None, 1, 1, 128, 0, 0, 1, None, 0, 0, None) == SHAPE
+    assert lib.actnn_pack_single(None, None, None, 2, None, None, None, 1, 1, 256, 1, 0, 1, None, 0, 0, None) == DTYPE
+    assert lib.actnn_pack_single(None, None, None, 2, None, None, None, 1, 1, 256, 0, 0, 1, None, 0, 0, None) == NULL
+    assert lib.actnn_pack_mixed(None, None, None, None, None, None, None, None, -1, 1, 256, 0, 0, 1, None, 0, 0, None) == SHAPE
+    assert lib.actnn_pack_mixed(None, None, None, None, None, None, None, None, 0, 1, 256, 0, 0, 1, None, 0, 0, None) == OK
+    assert lib.actnn_pack_mixed(None, None, None, None, None, None, None, None, 2, 1, 256, 0, 0, 1, None, 0, 0, None) == NULL
+    assert lib.actnn_unpack_mixed(None, None, None, None, None, None, 2, 1, 256, 2, 0, None) == DTYPE
+    assert lib.actnn_unpack_single(None, 8, None, None, None, 2, 1, 256, 0, 2, None) == NULL
+    # bit allocation
+    assert lib.actnn_calc_precision(None, None, 4, 1, 8.0, None, None, 0, 256, None) == BITS
+    assert lib.actnn_calc_precision(None, None, 4, 8, float("nan"), None, None, 0, 256, None) == ARG
+    assert lib.actnn_calc_precision(None, None, 4, 8, 8.0, None, None, 0, 256, None) == NULL
+    assert lib.actnn_bits_prefix(None, 4, 1, 100, None, None) == NULL
+    # mask ops
+    assert lib.actnn_relu_forward(None, None, None, -1, 0, None) == SHAPE
+    assert lib.actnn_relu_forward(None, None, None, 0, 0, None) == OK
+    assert lib.actnn_relu_forward(None, None, None, 5, 0, None) == NULL
+    assert lib.actnn_dropout_forward(None, None, None, 5, ctypes.c_float(1.5), 0, None, 0, 0, None) == ARG
+    assert lib.actnn_max_pool2d_forward(None, None, None, 1, 1, 8, 8, 4, 4, 1, 1, 0, 0, 1, 1, 0, None) == ARG
+    assert lib.actnn_max_pool2d_forward(None, None, None, 1, 1, 8, 8, 2, 2, 2, 2, 0, 0, 1, 1, 0, None) == NULL
+    assert lib.actnn_noise_fill(None, 8, 0, 1, 2, None) == NULL
+
+
+def test_missing_library_is_an_error(monkeypatch, tmp_path):
+    from actnn_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
+
+
+def test_calc_precision_has_no_cpu_path():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("only meaningful on a machine without a GPU")
+    from actnn_b200.cpp_extension import calc_precision
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        calc_precision.calc_precision(torch.ones(4, dtype=torch.int32) * 8, torch.ones(4),
+                                      torch.ones(4, dtype=torch.int32), 8)
+
+
+def test_package_api_surface():
+    import actnn_b200 as actnn
+    for name in ("set_optimization_level", "QModule", "QConv1d", "QConv2d", "QConv3d", "QConvTranspose2d",
+                 "QLinear", "QBatchNorm1d", "QBatchNorm2d", "QBatchNorm3d", "QSyncBatchNorm", "QReLU",
+                 "QDropout", "QMaxPool2d", "QScheme", "QBNScheme", "config"):
+        assert hasattr(actnn, name)
+    from actnn_b200.cpp_extension import backward_func, calc_precision, minimax, quantization
+    for fn in ("pack_mixed_precision", "unpack_mixed_precision", "pack_single_precision",
+               "unpack_single_precision", "act_quantized_relu", "act_quantized_dropout",
+               "act_quantized_max_pool2d"):
+        assert callable(getattr(quantization, fn))
+    assert callable(minimax.minimax) and callable(calc_precision.calc_precision)
+    assert callable(backward_func.cudnn_convolution_backward)
