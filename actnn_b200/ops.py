@@ -178,8 +178,9 @@ total_act_mem = 0
 
 
 def _autocast_inputs(*tensors):
-    """Under ``torch.autocast`` run the op in the autocast dtype, as a built-in op would."""
-    if not torch.is_autocast_enabled():
+    """Under ``torch.autocast`` run the op in the autocast dtype, as a built-in op would.
+    Must be called before autocast is switched off for the body of the Function."""
+    if not torch.is_autocast_enabled("cuda"):
         return tensors
     dt = torch.get_autocast_dtype("cuda")
     return tuple(t.to(dt) if isinstance(t, torch.Tensor) and t.is_floating_point() and t.is_cuda else t
@@ -212,8 +213,8 @@ class convnd(Function):
     @staticmethod
     def run_forward(n, forward_op, ctx, input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1,
                     scheme=None):
+        input, weight, bias = _autocast_inputs(input, weight, bias)
         with torch.autocast("cuda", enabled=False):
-            input, weight, bias = _autocast_inputs(input, weight, bias)
             quantized = quantize_activation(input, scheme)
             ctx.scheme = scheme
             ctx.saved = quantized, weight, bias
@@ -280,8 +281,8 @@ class conv_transposend(Function):
     @staticmethod
     def run_forward(n, forward_op, ctx, input, weight, bias=None, stride=1, padding=0, output_padding=0,
                     groups=1, dilation=1, scheme=None):
+        input, weight, bias = _autocast_inputs(input, weight, bias)
         with torch.autocast("cuda", enabled=False):
-            input, weight, bias = _autocast_inputs(input, weight, bias)
             quantized = quantize_activation(input, scheme)
             ctx.scheme = scheme
             ctx.saved = quantized, weight, bias
@@ -348,8 +349,8 @@ conv_transpose3d = _make_conv_transpose(3, F.conv_transpose3d, [0, 2, 3, 4], _tr
 class linear(Function):
     @staticmethod
     def forward(ctx, input, weight, bias=None, scheme=None):
+        input, weight, bias = _autocast_inputs(input, weight, bias)
         with torch.autocast("cuda", enabled=False):
-            input, weight, bias = _autocast_inputs(input, weight, bias)
             quantized = quantize_activation(input, scheme)
             empty_cache(config.empty_cache_threshold)
             ctx.scheme = scheme

@@ -379,14 +379,84 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------
+# profiling helper: a few launches of ONE kernel on a case that is larger than L2 but small
+# enough for a multi-pass ncu capture (float16 [512, 256, 28, 28] = 205 MB)
+# ---------------------------------------------------------------------------------------
+def run_profile(args):
+    import torch
+
+    from actnn_b200 import _lib
+    from actnn_b200.cpp_extension import calc_precision, minimax, quantization
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    N, G, gs, bits = 512, 784, 256, 2
+    dt = torch.float16
+    F16 = _lib.dtype_id(dt)
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(0)
+    x = torch.randn(N, G, gs, device=dev, dtype=dt)
+    out = torch.empty_like(x)
+    scale = torch.empty(N, G, 1, dtype=dt, device=dev)
+    mn = torch.empty(N, G, 1, dtype=dt, device=dev)
+    mx = torch.empty(N, G, 1, dtype=dt, device=dev)
+    packed = torch.empty(quantization.single_precision_bytes(bits, N, G, gs), dtype=torch.int8, device=dev)
+    Cs = torch.exp(torch.randn(N, device=dev))
+    bt, offs = calc_precision.allocate_bits(Cs, 8, 2 * N, None, G, gs, with_offsets=True)
+    pm = torch.empty(2 * N * G * gs // 32, dtype=torch.int32, device=dev)
+    mask = torch.empty((x.numel() + 31) // 32, dtype=torch.int32, device=dev)
+    lib.actnn_minimax(x.data_ptr(), mn.data_ptr(), mx.data_ptr(), N * G, gs, F16, st)
+    lib.actnn_compress_single(x.data_ptr(), bits, packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), None, N, G,
+                              gs, F16, F16, 1, None, 1, 0, st)
+    lib.actnn_pack_mixed(x.data_ptr(), mn.data_ptr(), mx.data_ptr(), bt.data_ptr(), offs.data_ptr(), pm.data_ptr(),
+                         scale.data_ptr(), None, N, G, gs, F16, F16, 1, None, 1, 0, st)
+    lib.actnn_relu_forward(x.data_ptr(), out.data_ptr(), mask.data_ptr(), x.numel(), F16, st)
+    calls = {
+        "compress_single": lambda: lib.actnn_compress_single(
+            x.data_ptr(), bits, packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), None, N, G, gs, F16, F16, 1,
+            None, 1, 0, st),
+        "unpack_single": lambda: lib.actnn_unpack_single(
+            packed.data_ptr(), bits, scale.data_ptr(), mn.data_ptr(), out.data_ptr(), N, G, gs, F16, F16, st),
+        "minimax": lambda: lib.actnn_minimax(x.data_ptr(), mn.data_ptr(), mx.data_ptr(), N * G, gs, F16, st),
+        "pack_mixed": lambda: lib.actnn_pack_mixed(
+            x.data_ptr(), mn.data_ptr(), mx.data_ptr(), bt.data_ptr(), offs.data_ptr(), pm.data_ptr(),
+            scale.data_ptr(), None, N, G, gs, F16, F16, 1, None, 1, 0, st),
+        "unpack_mixed": lambda: lib.actnn_unpack_mixed(
+            pm.data_ptr(), bt.data_ptr(), offs.data_ptr(), scale.data_ptr(), mn.data_ptr(), out.data_ptr(), N, G,
+            gs, F16, F16, st),
+        "relu_forward": lambda: lib.actnn_relu_forward(x.data_ptr(), out.data_ptr(), mask.data_ptr(), x.numel(),
+                                                       F16, st),
+        "relu_backward": lambda: lib.actnn_relu_backward(x.data_ptr(), mask.data_ptr(), out.data_ptr(), x.numel(),
+                                                        F16, st),
+    }
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    names = list(calls) if args.profile == "all" else [args.profile]
+    for name in names:
+        calls[name]()
+        a.record()
+        for _ in range(args.launches):
+            _lib.check(calls[name](), name)
+        b.record()
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": name, "shape": [N, G, gs], "dtype": "f16", "launches": args.launches,
+                          "ms_per_launch": round(a.elapsed_time(b) / args.launches, 5)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile", default=None, help="run a few launches of one kernel (for ncu); 'all' = each")
+    ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile:
+        run_profile(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

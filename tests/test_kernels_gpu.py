@@ -290,7 +290,7 @@ def test_dropout_forward_backward(ext, dtype):
 @pytest.mark.parametrize("geom", [((4, 8, 28, 28), (3, 3), (2, 2), (1, 1), (1, 1)),
                                   ((2, 3, 17, 9), (2, 2), (2, 2), (0, 0), (1, 1)),
                                   ((1, 2, 12, 13), (3, 2), (1, 2), (1, 0), (1, 1)),
-                                  ((2, 2, 15, 15), (3, 3), (2, 2), (2, 2), (2, 2))])
+                                  ((2, 2, 15, 15), (3, 3), (2, 2), (1, 1), (2, 2))])
 def test_max_pool2d_forward_backward(ext, dtype, geom):
     shape, k, s, p, d = geom
     x = make_input(shape, dtype, sum(shape))
@@ -299,7 +299,12 @@ def test_max_pool2d_forward_backward(ext, dtype, geom):
     assert same_values(y.cpu(), oy) and torch.equal(idx.cpu(), oidx)
     dy = make_input(tuple(y.shape), dtype, 11)
     dx = ext.q.max_pool2d_backward(dev(dy), idx, shape, k, s, p, d)
-    assert same_values(dx.cpu(), O.max_pool2d_backward(dy, oidx, shape, k, s, p, d))
+    # overlapping windows add up to four gradients per input; kernel and oracle sum them in
+    # float32 in different orders, so allow the last unit of the result type
+    odx = O.max_pool2d_backward(dy, oidx, shape, k, s, p, d)
+    tol = dict(rtol=1e-6, atol=1e-6) if dtype == torch.float32 else dict(rtol=8e-3, atol=1e-3)
+    assert torch.allclose(dx.cpu().float(), odx.float(), **tol)
+    assert torch.equal(dx.cpu() == 0, odx == 0)
     # against F.max_pool2d through autograd (reference test: 1e-4)
     a = dev(x).float().requires_grad_()
     torch.nn.functional.max_pool2d(a, k, s, p, d).backward(dev(dy).float())
