@@ -26,7 +26,7 @@ namespace {
 
 // One thread per octet of the padded [N, G, 256] activation.
 template <typename T>
-__global__ void noise_fill_kernel(T* __restrict__ out, int64_t numel, NoiseKey key) {
+__global__ void noise_fill_kernel(T* __restrict__ out, int64_t numel, const NoiseKey key) {
   const int64_t oct = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (oct * kOct >= numel) return;
   const uint64_t q = (uint64_t)(oct >> 5);        // 32 octets per 256-element group

@@ -24,108 +24,151 @@ struct BundleCoord {
   int g0, count;                      // first group within the sample, groups in this bundle
 };
 
-ACTNN_DEV BundleCoord bundle_coord(int64_t task, int64_t bundles_per_sample, int64_t G) {
-  BundleCoord c;
-  c.n = task / bundles_per_sample;
-  c.g0 = (int)(task - c.n * bundles_per_sample) * kBundle;
-  c.count = (int)min((int64_t)kBundle, G - c.g0);
-  c.q0 = c.n * G + c.g0;
-  return c;
-}
+// Walks the (sample, bundle-in-sample) pairs a warp owns without 64-bit divisions: the
+// stride between a warp's tasks is split once into whole samples and a remainder.
+struct BundleWalker {
+  int64_t n, N, G;
+  int r, bps, step_n, step_r, gpb;
+  ACTNN_DEV BundleWalker(int64_t warp, int64_t nwarps, int64_t N_, int64_t G_, int gpb_ = kBundle)
+      : N(N_), G(G_), gpb(gpb_) {
+    bps = (int)((G_ + gpb - 1) / gpb);
+    n = warp / bps;
+    r = (int)(warp - n * bps);
+    step_n = (int)(nwarps / bps);
+    step_r = (int)(nwarps - (int64_t)step_n * bps);
+  }
+  ACTNN_DEV bool valid() const { return n < N; }
+  ACTNN_DEV BundleCoord coord() const {
+    BundleCoord c;
+    c.n = n;
+    c.g0 = r * gpb;
+    c.count = (int)min((int64_t)gpb, G - c.g0);
+    c.q0 = n * G + c.g0;
+    return c;
+  }
+  ACTNN_DEV void next() {
+    n += step_n;
+    r += step_r;
+    if (r >= bps) { r -= bps; ++n; }
+  }
+};
 
 // ---------------------------------------------------------------------------- pack
-template <typename T, typename ST, int B>
-ACTNN_DEV void pack_bundle(const Oct<T> (&x)[kBundle], const Oct<T> (&nz)[kBundle], const BundleCoord& c,
-                           const T* __restrict__ mn, const T* __restrict__ mx, ST* __restrict__ scale,
-                           ST* __restrict__ mn_out, int32_t* __restrict__ out, const TransposePlan& plan,
-                           int lane) {
-  // lanes 0..3 prepare one group each, then broadcast
-  GroupParams mine = {0.f, 0.f};
-  if (lane < c.count) {
+// Groups per pack bundle: eight octets per lane for 16-bit types, four for float32.
+template <typename T> struct PackShape { static constexpr int GPB = sizeof(T) == 2 ? 8 : 4; };
+
+template <typename T, typename ST, int B, bool FULL>
+ACTNN_DEV void pack_bundle(const Oct<T> (&x)[PackShape<T>::GPB], const BundleCoord& c, const T* __restrict__ mn,
+                           const T* __restrict__ mx, ST* __restrict__ scale, ST* __restrict__ mn_out,
+                           int32_t* __restrict__ out, const T* __restrict__ noise, int stochastic,
+                           NoiseGen<T>& gen, const TransposePlan& plan, int lane) {
+  constexpr int GPB = PackShape<T>::GPB;
+  constexpr int W = GPB * 8 * B / 32;                    // words per lane string = transposes
+  const int count = FULL ? GPB : c.count;
+  // lane g (< count) prepares group g, then ships (mn', scale) to everyone
+  ParamWords mine = {0u, 0u};
+  if (lane < count) {
     const float gmn = load_scalar<T>(mn, c.q0 + lane), gmx = load_scalar<T>(mx, c.q0 + lane);
-    mine = prepare_group<T>(gmn, gmx, B);
-    store_scalar<ST>(scale, c.q0 + lane, mine.scale);
+    const GroupParams gp = prepare_group<T>(gmn, gmx, B);
+    store_scalar<ST>(scale, c.q0 + lane, gp.scale);
     if (mn_out) store_scalar<ST>(mn_out, c.q0 + lane, gmn);
+    mine = pack_params<T>(gp);
   }
-  uint32_t S[B];
+  uint32_t S[W];
 #pragma unroll
-  for (int k = 0; k < B; ++k) S[k] = 0u;
+  for (int k = 0; k < W; ++k) S[k] = 0u;
+  Oct<T> nzb[NoiseShape<T>::GPC];                     // one call's worth of noise octets
 #pragma unroll
-  for (int gi = 0; gi < kBundle; ++gi) {
-    GroupParams p;
-    p.mn1 = __shfl_sync(kFull, mine.mn1, gi);
-    p.scale = __shfl_sync(kFull, mine.scale, gi);
-    if (gi < c.count) {
-      uint32_t cp[4];
-      quantize_oct<T>(x[gi], nz[gi], p, B, cp);
-      if (gi == 0) put_codes<B, 0 * 8 * B>(S, cp);
-      if (gi == 1) put_codes<B, 1 * 8 * B>(S, cp);
-      if (gi == 2) put_codes<B, 2 * 8 * B>(S, cp);
-      if (gi == 3) put_codes<B, 3 * 8 * B>(S, cp);
+  for (int gi = 0; gi < GPB; ++gi) {
+    const QP<T> qp = fetch_params<T>(mine, gi);
+    if (FULL || gi < count) {
+      Oct<T> nz;
+      if (!stochastic) nz = zero_oct<T>();
+      else if (noise) nz = load_oct<T>(noise + (c.q0 + gi) * kGroup + lane * kOct);
+      else if (!FULL) nz = gen.get((uint64_t)(c.q0 + gi));
+      else {                                          // FULL: q0 is a multiple of the groups per call
+        if (gi % NoiseShape<T>::GPC == 0) noise_block<T>(gen.key, (uint64_t)(c.q0 + gi), lane, nzb);
+        nz = nzb[gi % NoiseShape<T>::GPC];
+      }
+      uint32_t lo, hi;
+      row_from_magic<T, B>(quantize_oct<T, true, B>(x[gi], nz, qp), lo, hi);
+      if (gi == 0) put_row<B, 0 * 8 * B>(S, lo, hi);
+      if (gi == 1) put_row<B, 1 * 8 * B>(S, lo, hi);
+      if (gi == 2) put_row<B, 2 * 8 * B>(S, lo, hi);
+      if (gi == 3) put_row<B, 3 * 8 * B>(S, lo, hi);
+      if constexpr (GPB > 4) {
+        if (gi == 4) put_row<B, 4 * 8 * B>(S, lo, hi);
+        if (gi == 5) put_row<B, 5 * 8 * B>(S, lo, hi);
+        if (gi == 6) put_row<B, 6 * 8 * B>(S, lo, hi);
+        if (gi == 7) put_row<B, 7 * 8 * B>(S, lo, hi);
+      }
     }
   }
-  const int words = c.count * 8 * B;
+  const int words = count * 8 * B;
 #pragma unroll
-  for (int k = 0; k < B; ++k) {
+  for (int k = 0; k < W; ++k) {
     const uint32_t y = warp_transpose32(S[k], plan);
     const int o = k * 32 + lane;
-    if (o < words) out[o] = (int32_t)y;
+    if (FULL || o < words) out[o] = (int32_t)y;
   }
 }
 
-template <typename T, typename ST>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, typename ST, bool FULL>
+__global__ void __launch_bounds__(kThreads, MagicInfo<T>::paired ? 3 : 2)
 pack_mixed_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T* __restrict__ mx,
                   const int32_t* __restrict__ bits, const int64_t* __restrict__ word_offsets,
                   int32_t* __restrict__ packed, ST* __restrict__ scale, ST* __restrict__ mn_out,
-                  int64_t N, int64_t G, const T* __restrict__ noise, int stochastic, NoiseKey key) {
+                  int64_t N, int64_t G, const T* __restrict__ noise, int stochastic, const NoiseKey key) {
+  constexpr int GPB = PackShape<T>::GPB;
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
-  const int64_t bps = (G + kBundle - 1) / kBundle;
-  const int64_t total = N * bps;
   const TransposePlan plan = make_transpose_plan(lane);
   NoiseGen<T> gen(key, lane);
 
-  for (int64_t task = warp; task < total; task += nwarps) {
-    const BundleCoord c = bundle_coord(task, bps, G);
-    Oct<T> x[kBundle], nz[kBundle];
+  for (BundleWalker walk(warp, nwarps, N, G, GPB); walk.valid(); walk.next()) {
+    const BundleCoord c = walk.coord();
+    Oct<T> x[GPB];
 #pragma unroll
-    for (int gi = 0; gi < kBundle; ++gi)
-      x[gi] = gi < c.count ? load_oct<T>(data + (c.q0 + gi) * kGroup + lane * kOct) : zero_oct<T>();
+    for (int gi = 0; gi < GPB; ++gi)
+      x[gi] = (FULL || gi < c.count) ? load_oct<T>(data + (c.q0 + gi) * kGroup + lane * kOct) : zero_oct<T>();
     const int b = __ldg(bits + c.n);
-    const int64_t base = __ldg(word_offsets + c.n) + (int64_t)c.g0 * 8 * b;
-#pragma unroll
-    for (int gi = 0; gi < kBundle; ++gi) {
-      if (!stochastic || gi >= c.count) nz[gi] = zero_oct<T>();
-      else if (noise) nz[gi] = load_oct<T>(noise + (c.q0 + gi) * kGroup + lane * kOct);
-      else nz[gi] = gen.get((uint64_t)(c.q0 + gi));
-    }
-    int32_t* out = packed + base;
+    int32_t* out = packed + (__ldg(word_offsets + c.n) + (int64_t)c.g0 * 8 * b);
+#define ACTNN_CASE(B)                                                                                     \
+    case B:                                                                                               \
+      pack_bundle<T, ST, B, FULL>(x, c, mn, mx, scale, mn_out, out, noise, stochastic, gen, plan, lane);  \
+      break;
     switch (b) {
-      case 1: pack_bundle<T, ST, 1>(x, nz, c, mn, mx, scale, mn_out, out, plan, lane); break;
-      case 2: pack_bundle<T, ST, 2>(x, nz, c, mn, mx, scale, mn_out, out, plan, lane); break;
-      case 3: pack_bundle<T, ST, 3>(x, nz, c, mn, mx, scale, mn_out, out, plan, lane); break;
-      case 4: pack_bundle<T, ST, 4>(x, nz, c, mn, mx, scale, mn_out, out, plan, lane); break;
-      case 5: pack_bundle<T, ST, 5>(x, nz, c, mn, mx, scale, mn_out, out, plan, lane); break;
-      case 6: pack_bundle<T, ST, 6>(x, nz, c, mn, mx, scale, mn_out, out, plan, lane); break;
-      case 7: pack_bundle<T, ST, 7>(x, nz, c, mn, mx, scale, mn_out, out, plan, lane); break;
-      case 8: pack_bundle<T, ST, 8>(x, nz, c, mn, mx, scale, mn_out, out, plan, lane); break;
+      ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
+      ACTNN_CASE(8)
       default: break;     // widths outside 1..8 are skipped; the host documents the range
     }
+#undef ACTNN_CASE
   }
 }
 
 // ---------------------------------------------------------------------------- unpack
+// Decoding a group needs only 2^B distinct outputs, code / scale + min for code = 0..2^B-1.
+// Lanes compute those once (one IEEE division per lane for up to four groups at a time)
+// and the elements look theirs up: for 16-bit types and B <= 2 the table of a group fits
+// two registers and a byte-permute picks two elements per instruction; otherwise a warp
+// shuffle fetches the entry; from 6 bits on the division is done per element.
+template <int B> ACTNN_DEV uint32_t spread_codes_to_bytes(uint32_t r) {   // four B-bit codes -> one per byte
+  if constexpr (B == 2) {
+    uint32_t t = (r | (r << 12)) & 0x000f000fu;
+    return (t | (t << 6)) & 0x03030303u;
+  } else {
+    uint32_t t = (r | (r << 14)) & 0x00030003u;
+    return (t | (t << 7)) & 0x01010101u;
+  }
+}
+
 template <typename T, typename ST, int B>
 ACTNN_DEV void unpack_bundle(const int32_t* __restrict__ in, const BundleCoord& c,
                              const ST* __restrict__ scale, const ST* __restrict__ mn, T* __restrict__ out,
                              const TransposePlan& plan, int lane) {
-  float my_scale = 1.f, my_mn = 0.f;
-  if (lane < c.count) {
-    my_scale = load_scalar<ST>(scale, c.q0 + lane);
-    my_mn = load_scalar<ST>(mn, c.q0 + lane);
-  }
+  constexpr int E = 1 << (B < 6 ? B : 5);              // table entries per group
+  constexpr int GPC = (32 / E) < kBundle ? (32 / E) : kBundle;   // groups served by one table computation
   const int words = c.count * 8 * B;
   uint32_t S[B];
 #pragma unroll
@@ -134,54 +177,85 @@ ACTNN_DEV void unpack_bundle(const int32_t* __restrict__ in, const BundleCoord& 
     const uint32_t w = o < words ? (uint32_t)__ldg(in + o) : 0u;
     S[k] = warp_transpose32(w, plan);
   }
+  float stat_scale = 1.f, stat_mn = 0.f;               // B >= 6: lane l holds the statistics of group l
+  if constexpr (B >= 6) {
+    if (lane < c.count) {
+      stat_scale = load_scalar<ST>(scale, c.q0 + lane);
+      stat_mn = load_scalar<ST>(mn, c.q0 + lane);
+    }
+  }
+  uint32_t entry = 0u, pairs = 0u;
 #pragma unroll
   for (int gi = 0; gi < kBundle; ++gi) {
-    const float sc = __shfl_sync(kFull, my_scale, gi);
-    const float m = __shfl_sync(kFull, my_mn, gi);
-    uint32_t code[8];
-    if (gi == 0) get_codes<B, 0 * 8 * B>(S, code);
-    if (gi == 1) get_codes<B, 1 * 8 * B>(S, code);
-    if (gi == 2) get_codes<B, 2 * 8 * B>(S, code);
-    if (gi == 3) get_codes<B, 3 * 8 * B>(S, code);
-    uint32_t v[8];
-    if constexpr (B <= 5) {
-      // 2^B distinct outputs per group: lane k computes the one for code k (one IEEE
-      // division per lane instead of eight), elements fetch theirs with a shuffle
-      const uint32_t entry = dequant_bits<T>((float)lane, sc, m);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = __shfl_sync(kFull, entry, (int)code[j]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = dequant_bits<T>((float)code[j], sc, m);
+    if constexpr (B < 6) {
+      if (gi % GPC == 0) {                               // (re)build the table for groups gi .. gi+GPC-1
+        const int g = gi + lane / E;
+        float sc = 1.f, m = 0.f;
+        if (lane < GPC * E && g < c.count) {
+          sc = load_scalar<ST>(scale, c.q0 + g);
+          m = load_scalar<ST>(mn, c.q0 + g);
+        }
+        entry = dequant_bits<T>((float)(lane % E), sc, m);
+        if constexpr (sizeof(T) == 2 && B <= 2)
+          pairs = entry | (__shfl_down_sync(kFull, entry, 1) << 16);
+      }
     }
-    if (gi < c.count) {
-      Oct<T> o;
+    uint32_t lo = 0u, hi = 0u;                           // this group's row
+    if (gi == 0) { lo = get_bits<0 * 8 * B, (8 * B < 32 ? 8 * B : 32)>(S); if constexpr (8 * B > 32) hi = get_bits<0 * 8 * B + 32, 8 * B - 32>(S); }
+    if (gi == 1) { lo = get_bits<1 * 8 * B, (8 * B < 32 ? 8 * B : 32)>(S); if constexpr (8 * B > 32) hi = get_bits<1 * 8 * B + 32, 8 * B - 32>(S); }
+    if (gi == 2) { lo = get_bits<2 * 8 * B, (8 * B < 32 ? 8 * B : 32)>(S); if constexpr (8 * B > 32) hi = get_bits<2 * 8 * B + 32, 8 * B - 32>(S); }
+    if (gi == 3) { lo = get_bits<3 * 8 * B, (8 * B < 32 ? 8 * B : 32)>(S); if constexpr (8 * B > 32) hi = get_bits<3 * 8 * B + 32, 8 * B - 32>(S); }
+    Oct<T> o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+    if constexpr (sizeof(T) == 2 && B <= 2) {
+      const int base = (gi % GPC) * E;
+      const uint32_t t01 = __shfl_sync(kFull, pairs, base);
+      const uint32_t t23 = B == 2 ? __shfl_sync(kFull, pairs, base + 2) : t01;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                      // four elements per step
+        const uint32_t y = spread_codes_to_bytes<B>((lo >> (4 * B * h)) & ((1u << (4 * B)) - 1u));
+        const uint32_t sel = y * 0x22u + 0x10101010u;    // byte pair (2c, 2c+1) per element
+        ow[2 * h] = __byte_perm(t01, t23, sel);
+        ow[2 * h + 1] = __byte_perm(t01, t23, sel >> 16);
+      }
+    } else {
+      uint32_t v[8];
+      const uint32_t S2[2] = {lo, hi};
+      uint32_t code[8];
+      get_codes<B, 0>(S2, code);
+      if constexpr (B < 6) {
+        const int base = (gi % GPC) * E;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __shfl_sync(kFull, entry, base + (int)code[j]);
+      } else {
+        const float sc = __shfl_sync(kFull, stat_scale, gi), m = __shfl_sync(kFull, stat_mn, gi);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = dequant_bits<T>((float)code[j], sc, m);
+      }
       if constexpr (sizeof(T) == 4) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) reinterpret_cast<uint32_t*>(&o)[j] = v[j];
+        for (int j = 0; j < 8; ++j) ow[j] = v[j];
       } else {
 #pragma unroll
-        for (int mth = 0; mth < 4; ++mth) reinterpret_cast<uint32_t*>(&o)[mth] = v[2 * mth] | (v[2 * mth + 1] << 16);
+        for (int k = 0; k < 4; ++k) ow[k] = v[2 * k] | (v[2 * k + 1] << 16);
       }
-      store_oct<T>(out + (c.q0 + gi) * kGroup + lane * kOct, o);
     }
+    if (gi < c.count) store_oct<T>(out + (c.q0 + gi) * kGroup + lane * kOct, o);
   }
 }
 
 template <typename T, typename ST>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 unpack_mixed_kernel(const int32_t* __restrict__ packed, const int32_t* __restrict__ bits,
                     const int64_t* __restrict__ word_offsets, const ST* __restrict__ scale,
                     const ST* __restrict__ mn, T* __restrict__ out, int64_t N, int64_t G) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
-  const int64_t bps = (G + kBundle - 1) / kBundle;
-  const int64_t total = N * bps;
   const TransposePlan plan = make_transpose_plan(lane);
 
-  for (int64_t task = warp; task < total; task += nwarps) {
-    const BundleCoord c = bundle_coord(task, bps, G);
+  for (BundleWalker walk(warp, nwarps, N, G); walk.valid(); walk.next()) {
+    const BundleCoord c = walk.coord();
     const int b = __ldg(bits + c.n);
     const int32_t* in = packed + __ldg(word_offsets + c.n) + (int64_t)c.g0 * 8 * b;
     switch (b) {
@@ -238,21 +312,24 @@ bits_prefix_kernel(const int32_t* __restrict__ bits, int64_t N, int64_t words_pe
   if (threadIdx.x == 0) word_offsets[N] = carry * words_per_bit;
 }
 
-int grid_for(int64_t warp_tasks) {
-  const int64_t blocks = (warp_tasks + (kThreads / 32) - 1) / (kThreads / 32);
-  const int64_t cap = (int64_t)device_info().sm_count * 8;      // 8 x 256 threads fill an SM
-  return (int)max((int64_t)1, min(blocks, cap));
-}
-
 template <typename T, typename ST>
 int launch_pack(const void* data, const void* mn, const void* mx, const int32_t* bits,
                 const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out, int64_t N,
                 int64_t G, int stochastic, const void* noise, uint64_t seed, uint64_t offset,
                 cudaStream_t stream) {
-  const int64_t tasks = N * ((G + kBundle - 1) / kBundle);
-  pack_mixed_kernel<T, ST><<<grid_for(tasks), kThreads, 0, stream>>>(
-      (const T*)data, (const T*)mn, (const T*)mx, bits, word_offsets, packed, (ST*)scale, (ST*)mn_out, N, G,
-      (const T*)noise, stochastic, make_noise_key(seed, offset));
+  constexpr int GPB = PackShape<T>::GPB;
+  const int64_t tasks = N * ((G + GPB - 1) / GPB);
+  const NoiseKey key = make_noise_key(seed, offset);
+  if (G % GPB == 0)
+    pack_mixed_kernel<T, ST, true><<<persistent_grid(pack_mixed_kernel<T, ST, true>, kThreads, tasks), kThreads, 0,
+                                     stream>>>(
+        (const T*)data, (const T*)mn, (const T*)mx, bits, word_offsets, packed, (ST*)scale, (ST*)mn_out, N, G,
+        (const T*)noise, stochastic, key);
+  else
+    pack_mixed_kernel<T, ST, false><<<persistent_grid(pack_mixed_kernel<T, ST, false>, kThreads, tasks), kThreads, 0,
+                                      stream>>>(
+        (const T*)data, (const T*)mn, (const T*)mx, bits, word_offsets, packed, (ST*)scale, (ST*)mn_out, N, G,
+        (const T*)noise, stochastic, key);
   return check_launch();
 }
 
@@ -260,7 +337,7 @@ template <typename T, typename ST>
 int launch_unpack(const int32_t* packed, const int32_t* bits, const int64_t* word_offsets,
                   const void* scale, const void* mn, void* out, int64_t N, int64_t G, cudaStream_t stream) {
   const int64_t tasks = N * ((G + kBundle - 1) / kBundle);
-  unpack_mixed_kernel<T, ST><<<grid_for(tasks), kThreads, 0, stream>>>(
+  unpack_mixed_kernel<T, ST><<<persistent_grid(unpack_mixed_kernel<T, ST>, kThreads, tasks), kThreads, 0, stream>>>(
       packed, bits, word_offsets, (const ST*)scale, (const ST*)mn, (T*)out, N, G);
   return check_launch();
 }

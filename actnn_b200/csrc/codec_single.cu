@@ -15,168 +15,236 @@ namespace actnn {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kPair = 2;              // groups per warp task
 
-template <typename T, typename ST, int BITS, bool FUSED>
-__global__ void __launch_bounds__(kThreads)
+// Byte accumulators for one group: sample ni's magic registers are added in shifted left
+// by ni*BITS.  The exponent bits of the rounding constant add up to a compile-time
+// constant that is subtracted up front, so no per-code masking is needed.
+template <typename T, int BITS> struct ByteAcc {
+  static constexpr int WPT = 8 / BITS;
+  static constexpr int R = MagicInfo<T>::paired ? 4 : 8;
+  uint32_t a[R];
+  ACTNN_DEV ByteAcc() {
+#pragma unroll
+    for (int i = 0; i < R; ++i) a[i] = 0u - shifted_sum(MagicInfo<T>::bias, BITS, WPT);
+  }
+  template <int NI> ACTNN_DEV void add(const Magic<T>& m) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) a[i] += m.v[i] << (NI * BITS);
+  }
+  template <int NI> ACTNN_DEV void add_missing() {       // a sample past the end: code 0 everywhere
+#pragma unroll
+    for (int i = 0; i < R; ++i) a[i] += MagicInfo<T>::bias << (NI * BITS);
+  }
+  ACTNN_DEV uint2 bytes() const {
+    uint2 w;
+    if constexpr (MagicInfo<T>::paired) {                // a[k] = byte 2k | byte 2k+1 << 16
+      w.x = __byte_perm(a[0], a[1], 0x6420);
+      w.y = __byte_perm(a[2], a[3], 0x6420);
+    } else {                                             // a[j] = byte j
+      w.x = a[0] + (a[1] << 8) + (a[2] << 16) + (a[3] << 24);
+      w.y = a[4] + (a[5] << 8) + (a[6] << 16) + (a[7] << 24);
+    }
+    return w;
+  }
+};
+
+// Walks (sample block, group pair) tasks without 64-bit divisions.
+struct PairWalker {
+  int64_t no, blocks;
+  int r, per, step_n, step_r;
+  ACTNN_DEV PairWalker(int64_t warp, int64_t nwarps, int64_t blocks_, int64_t per_) : blocks(blocks_) {
+    per = (int)per_;
+    no = warp / per;
+    r = (int)(warp - no * per);
+    step_n = (int)(nwarps / per);
+    step_r = (int)(nwarps - (int64_t)step_n * per);
+  }
+  ACTNN_DEV bool valid() const { return no < blocks; }
+  ACTNN_DEV void next() {
+    no += step_n;
+    r += step_r;
+    if (r >= per) { r -= per; ++no; }
+  }
+};
+
+// Shape of one warp task.  A task covers GP neighbouring groups of one block of wpt
+// samples and is worked off in ROUNDS rounds of SS samples; a round holds OCTS = SS * GP
+// octets per lane in registers.  All their group statistics are prepared together: lane o
+// (< OCTS) owns octet o = s * GP + gi, does the one division, and ships the result.
+template <typename T, int BITS> struct TaskShape {
+  static constexpr int WPT = 8 / BITS;
+  static constexpr int OCTS = sizeof(T) == 2 ? 8 : 4;
+  // at least one Philox call's worth of neighbouring groups (4 for 16-bit types, 2 for float32)
+  static constexpr int SS = WPT < 2 ? 1 : 2;
+  static constexpr int GP = OCTS / SS;
+  static constexpr int ROUNDS = WPT / SS;
+};
+
+template <typename T, typename ST, int BITS, bool FUSED, bool FULL>
+__global__ void __launch_bounds__(kThreads, MagicInfo<T>::paired ? 3 : 2)
 pack_single_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T* __restrict__ mx,
                    int8_t* __restrict__ packed, ST* __restrict__ scale, ST* __restrict__ mn_out,
                    ST* __restrict__ mx_out, int64_t N, int64_t G, const T* __restrict__ noise,
-                   int stochastic, NoiseKey key, int64_t total_bytes) {
-  constexpr int WPT = 8 / BITS;
+                   int stochastic, const NoiseKey key, int64_t total_bytes) {
+  using Sh = TaskShape<T, BITS>;
+  constexpr int WPT = Sh::WPT, OCTS = Sh::OCTS, SS = Sh::SS, GP = Sh::GP, ROUNDS = Sh::ROUNDS;
+  static_assert(GP % NoiseShape<T>::GPC == 0, "a task covers whole Philox calls");
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
-  const int64_t gpairs = (G + kPair - 1) / kPair;
+  const int64_t gblocks = (G + GP - 1) / GP;
   const int64_t nblocks = (N + WPT - 1) / WPT;
-  const int64_t total = nblocks * gpairs;
   NoiseGen<T> gen(key, lane);
   if (warp == 0 && lane == 0) packed[total_bytes - 1] = 0;     // the reference's spare byte
+  // the octet this lane prepares statistics for
+  const int my_s = lane / GP, my_gi = lane % GP;
 
-  for (int64_t task = warp; task < total; task += nwarps) {
-    const int64_t no = task / gpairs;
-    const int64_t g0 = (task - no * gpairs) * kPair;
-    const int cnt = (int)min((int64_t)kPair, G - g0);
-    uint32_t acc[kPair][4];
-#pragma unroll
-    for (int gi = 0; gi < kPair; ++gi)
-#pragma unroll
-      for (int m = 0; m < 4; ++m) acc[gi][m] = 0u;
+  for (PairWalker walk(warp, nwarps, nblocks, gblocks); walk.valid(); walk.next()) {
+    const int64_t no = walk.no;
+    const int64_t g0 = (int64_t)walk.r * GP;
+    const int cnt = FULL ? GP : (int)min((int64_t)GP, G - g0);
+    ByteAcc<T, BITS> acc[GP];
 
 #pragma unroll
-    for (int ni = 0; ni < WPT; ni += 2) {
-      // two samples x two groups in flight
-      Oct<T> x[2][kPair];
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+      const int64_t n0 = no * WPT + rd * SS;
+      Oct<T> x[OCTS];
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const int64_t n = no * WPT + ni + s;
-#pragma unroll
-        for (int gi = 0; gi < kPair; ++gi)
-          x[s][gi] = (s < WPT && n < N && gi < cnt)
-                         ? load_oct<T>(data + (n * G + g0 + gi) * kGroup + lane * kOct) : zero_oct<T>();
+      for (int o = 0; o < OCTS; ++o) {
+        const int s = o / GP, gi = o % GP;
+        const bool ok = FULL || (n0 + s < N && gi < cnt);
+        x[o] = ok ? load_oct<T>(data + ((n0 + s) * G + g0 + gi) * kGroup + lane * kOct) : zero_oct<T>();
       }
+      // ---- statistics of the OCTS groups, one per lane
+      float gmn = 0.f, gmx = 0.f;
+      const bool mine_ok = lane < OCTS && (FULL || (n0 + my_s < N && my_gi < cnt));
+      const int64_t my_q = (n0 + my_s) * G + g0 + my_gi;
+      if constexpr (FUSED) {
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        if (ni + s >= WPT) continue;
-        const int64_t n = no * WPT + ni + s;
-        if (n >= N) continue;                                   // warp-uniform
-        const int64_t q0 = n * G + g0;
-        // group statistics: lanes 0..1 own one group each
-        float gmn = 0.f, gmx = 0.f;
-        if constexpr (FUSED) {
-          float a[kPair], b[kPair];
-#pragma unroll
-          for (int gi = 0; gi < kPair; ++gi) {
-            float lo, hi;
-            oct_minmax<T>(x[s][gi], lo, hi);
-            a[gi] = warp_min(lo);
-            b[gi] = warp_max(hi);
-          }
-          gmn = lane == 0 ? a[0] : a[1];
-          gmx = lane == 0 ? b[0] : b[1];
-        } else if (lane < cnt) {
-          gmn = load_scalar<T>(mn, q0 + lane);
-          gmx = load_scalar<T>(mx, q0 + lane);
+        for (int o = 0; o < OCTS; ++o) {
+          float lo, hi;
+          oct_minmax<T>(x[o], lo, hi);
+          lo = warp_min(lo);
+          hi = warp_max(hi);
+          if (lane == o) { gmn = lo; gmx = hi; }
         }
-        GroupParams mine = {0.f, 0.f};
-        if (lane < cnt) {
-          mine = prepare_group<T>(gmn, gmx, BITS);
-          store_scalar<ST>(scale, q0 + lane, mine.scale);
-          if (mn_out) store_scalar<ST>(mn_out, q0 + lane, gmn);
-          if (FUSED && mx_out) store_scalar<ST>(mx_out, q0 + lane, gmx);
-        }
+      } else if (mine_ok) {
+        gmn = load_scalar<T>(mn, my_q);
+        gmx = load_scalar<T>(mx, my_q);
+      }
+      ParamWords mine = {0u, 0u};
+      if (mine_ok) {
+        const GroupParams gp = prepare_group<T>(gmn, gmx, BITS);
+        store_scalar<ST>(scale, my_q, gp.scale);
+        if (mn_out) store_scalar<ST>(mn_out, my_q, gmn);
+        if (FUSED && mx_out) store_scalar<ST>(mx_out, my_q, gmx);
+        mine = pack_params<T>(gp);
+      }
+      // ---- quantize and merge into the byte accumulators
+      Oct<T> nzb[NoiseShape<T>::GPC];                   // one call's worth of noise octets
 #pragma unroll
-        for (int gi = 0; gi < kPair; ++gi) {
-          GroupParams p;
-          p.mn1 = __shfl_sync(kFull, mine.mn1, gi);
-          p.scale = __shfl_sync(kFull, mine.scale, gi);
-          if (gi < cnt) {
-            Oct<T> nz;
-            if (!stochastic) nz = zero_oct<T>();
-            else if (noise) nz = load_oct<T>(noise + (q0 + gi) * kGroup + lane * kOct);
-            else nz = gen.get((uint64_t)(q0 + gi));
-            uint32_t cp[4];
-            quantize_oct<T>(x[s][gi], nz, p, BITS, cp);
-#pragma unroll
-            for (int m = 0; m < 4; ++m) acc[gi][m] |= cp[m] << ((ni + s) * BITS);
-          }
+      for (int o = 0; o < OCTS; ++o) {
+        const int s = o / GP, gi = o % GP;
+        const QP<T> qp = fetch_params<T>(mine, o);
+        const bool ok = FULL || (n0 + s < N && gi < cnt);
+        Oct<T> nz;
+        const int64_t q = (n0 + s) * G + g0 + gi;
+        if (!stochastic || !ok) nz = zero_oct<T>();
+        else if (noise) nz = load_oct<T>(noise + q * kGroup + lane * kOct);
+        else if (!FULL) nz = gen.get((uint64_t)q);
+        else {                                          // FULL: q - gi is a multiple of the groups per call
+          if (gi % NoiseShape<T>::GPC == 0) noise_block<T>(gen.key, (uint64_t)q, lane, nzb);
+          nz = nzb[gi % NoiseShape<T>::GPC];
         }
+        // with the true minimum in hand the low clamp is implied by the rounding
+        const Magic<T> m = quantize_oct<T, !FUSED, BITS>(x[o], nz, qp);
+#define ACTNN_ADD(K)                                                               \
+        if constexpr (K < WPT) {                                                   \
+          if (rd * SS + s == K) {                                                  \
+            if (ok) acc[gi].template add<K>(m);                                    \
+            else acc[gi].template add_missing<K>();                                \
+          }                                                                        \
+        }
+        ACTNN_ADD(0) ACTNN_ADD(1) ACTNN_ADD(2) ACTNN_ADD(3) ACTNN_ADD(4) ACTNN_ADD(5) ACTNN_ADD(6) ACTNN_ADD(7)
+#undef ACTNN_ADD
       }
     }
-    // acc[gi][m] holds byte 2m in its low half and byte 2m+1 in its high half
 #pragma unroll
-    for (int gi = 0; gi < kPair; ++gi) {
-      if (gi < cnt) {
-        uint2 w;
-        w.x = __byte_perm(acc[gi][0], acc[gi][1], 0x6420);
-        w.y = __byte_perm(acc[gi][2], acc[gi][3], 0x6420);
-        *reinterpret_cast<uint2*>(packed + ((no * G + g0 + gi) * kGroup + lane * kOct)) = w;
-      }
+    for (int gi = 0; gi < GP; ++gi) {
+      if (FULL || gi < cnt)
+        *reinterpret_cast<uint2*>(packed + ((no * G + g0 + gi) * kGroup + lane * kOct)) = acc[gi].bytes();
     }
   }
 }
 
+// Unpack: a warp owns (sample block, group).  Lane t reads its eight bytes once; the table
+// of all wpt samples x 2^BITS codes is computed by the first wpt * 2^BITS lanes together
+// (one IEEE division per lane), and for 16-bit outputs with BITS <= 2 a byte-permute
+// selects two decoded elements per instruction.
 template <typename T, typename ST, int BITS>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 unpack_single_kernel(const int8_t* __restrict__ packed, const ST* __restrict__ scale,
                      const ST* __restrict__ mn, T* __restrict__ out, int64_t N, int64_t G) {
   constexpr int WPT = 8 / BITS;
+  constexpr int E = 1 << BITS;
+  constexpr bool TABLE = BITS <= 4;                        // BITS == 8: divide per element
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const int64_t nblocks = (N + WPT - 1) / WPT;
-  const int64_t total = nblocks * G;
 
-  for (int64_t task = warp; task < total; task += nwarps) {
-    const int64_t no = task / G;
-    const int64_t g = task - no * G;
+  for (PairWalker walk(warp, nwarps, nblocks, G); walk.valid(); walk.next()) {
+    const int64_t no = walk.no;
+    const int64_t g = walk.r;
     const uint2 w = __ldg(reinterpret_cast<const uint2*>(packed + ((no * G + g) * kGroup + lane * kOct)));
-    // lane ni (< wpt) fetches the statistics of sample no*wpt + ni
-    const int64_t my_n = no * WPT + (lane < WPT ? lane : 0);
-    float my_scale = 1.f, my_mn = 0.f;
-    if (lane < WPT && my_n < N) {
-      my_scale = load_scalar<ST>(scale, my_n * G + g);
-      my_mn = load_scalar<ST>(mn, my_n * G + g);
+    // lane l serves sample no*wpt + l / E (TABLE) or sample no*wpt + l (BITS == 8)
+    const int my_s = TABLE ? lane / E : lane;
+    const int64_t my_n = no * WPT + my_s;
+    float sc = 1.f, m = 0.f;
+    if (my_s < WPT && my_n < N) {
+      sc = load_scalar<ST>(scale, my_n * G + g);
+      m = load_scalar<ST>(mn, my_n * G + g);
+    }
+    uint32_t entry = 0u, pairs = 0u;
+    if constexpr (TABLE) {
+      entry = dequant_bits<T>((float)(lane % E), sc, m);
+      if constexpr (sizeof(T) == 2 && BITS <= 2) pairs = entry | (__shfl_down_sync(kFull, entry, 1) << 16);
     }
 #pragma unroll
     for (int ni = 0; ni < WPT; ++ni) {
       const int64_t n = no * WPT + ni;
-      const float sc = __shfl_sync(kFull, my_scale, ni);
-      const float m = __shfl_sync(kFull, my_mn, ni);
-      uint32_t v[8];
-      if constexpr (BITS <= 4) {
-        const uint32_t entry = dequant_bits<T>((float)lane, sc, m);
+      Oct<T> o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+      if constexpr (sizeof(T) == 2 && BITS <= 2) {
+        const uint32_t t01 = __shfl_sync(kFull, pairs, ni * E);
+        const uint32_t t23 = BITS == 2 ? __shfl_sync(kFull, pairs, ni * E + 2) : t01;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t byte = ((j < 4 ? w.x : w.y) >> (8 * (j & 3))) & 0xffu;
-          v[j] = __shfl_sync(kFull, entry, (int)((byte >> (ni * BITS)) & ((1u << BITS) - 1u)));
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t y = ((h ? w.y : w.x) >> (ni * BITS)) & (0x01010101u * (uint32_t)(E - 1));
+          const uint32_t sel = y * 0x22u + 0x10101010u;
+          ow[2 * h] = __byte_perm(t01, t23, sel);
+          ow[2 * h + 1] = __byte_perm(t01, t23, sel >> 16);
         }
       } else {
+        uint32_t v[8];
+        const float sc_n = TABLE ? 0.f : __shfl_sync(kFull, sc, ni), m_n = TABLE ? 0.f : __shfl_sync(kFull, m, ni);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint32_t byte = ((j < 4 ? w.x : w.y) >> (8 * (j & 3))) & 0xffu;
-          v[j] = dequant_bits<T>((float)byte, sc, m);
+          const uint32_t code = ((((j < 4) ? w.x : w.y) >> (8 * (j & 3))) >> (ni * BITS)) & (uint32_t)(E - 1);
+          if constexpr (TABLE) v[j] = __shfl_sync(kFull, entry, ni * E + (int)code);
+          else v[j] = dequant_bits<T>((float)code, sc_n, m_n);
         }
-      }
-      if (n < N) {
-        Oct<T> o;
         if constexpr (sizeof(T) == 4) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) reinterpret_cast<uint32_t*>(&o)[j] = v[j];
+          for (int j = 0; j < 8; ++j) ow[j] = v[j];
         } else {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) reinterpret_cast<uint32_t*>(&o)[k] = v[2 * k] | (v[2 * k + 1] << 16);
+          for (int k = 0; k < 4; ++k) ow[k] = v[2 * k] | (v[2 * k + 1] << 16);
         }
-        store_oct<T>(out + (n * G + g) * kGroup + lane * kOct, o);
       }
+      if (n < N) store_oct<T>(out + (n * G + g) * kGroup + lane * kOct, o);
     }
   }
-}
-
-int grid_for(int64_t warp_tasks) {
-  const int64_t blocks = (warp_tasks + (kThreads / 32) - 1) / (kThreads / 32);
-  const int64_t cap = (int64_t)device_info().sm_count * 8;
-  return (int)max((int64_t)1, min(blocks, cap));
 }
 
 int64_t single_total_bytes(int bits, int64_t N, int64_t G) {
@@ -189,15 +257,25 @@ template <typename T, typename ST, bool FUSED>
 int launch_pack(int bits, const void* data, const void* mn, const void* mx, int8_t* packed, void* scale,
                 void* mn_out, void* mx_out, int64_t N, int64_t G, int stochastic, const void* noise,
                 uint64_t seed, uint64_t offset, cudaStream_t s) {
-  const int wpt = 8 / bits;
-  const int64_t tasks = ((N + wpt - 1) / wpt) * ((G + kPair - 1) / kPair);
-  const int grid = grid_for(tasks);
   const NoiseKey key = make_noise_key(seed, offset);
   const int64_t tb = single_total_bytes(bits, N, G);
-#define ACTNN_LAUNCH(BITS)                                                                        \
-  pack_single_kernel<T, ST, BITS, FUSED><<<grid, kThreads, 0, s>>>(                               \
-      (const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, (ST*)mn_out, (ST*)mx_out, N, G, \
-      (const T*)noise, stochastic, key, tb)
+#define ACTNN_LAUNCH(BITS)                                                                          \
+  {                                                                                                 \
+    using Sh = TaskShape<T, BITS>;                                                                  \
+    const int64_t tasks = ((N + Sh::WPT - 1) / Sh::WPT) * ((G + Sh::GP - 1) / Sh::GP);              \
+    /* whole tasks only, each starting on a Philox call boundary */                                \
+    const bool full = N % Sh::WPT == 0 && G % Sh::GP == 0;                                          \
+    const int grid = full ? persistent_grid(pack_single_kernel<T, ST, BITS, FUSED, true>, kThreads, tasks)   \
+                          : persistent_grid(pack_single_kernel<T, ST, BITS, FUSED, false>, kThreads, tasks); \
+    if (full)                                                                                       \
+      pack_single_kernel<T, ST, BITS, FUSED, true><<<grid, kThreads, 0, s>>>(                       \
+          (const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, (ST*)mn_out, (ST*)mx_out, N, G, \
+          (const T*)noise, stochastic, key, tb);                                                    \
+    else                                                                                            \
+      pack_single_kernel<T, ST, BITS, FUSED, false><<<grid, kThreads, 0, s>>>(                      \
+          (const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, (ST*)mn_out, (ST*)mx_out, N, G, \
+          (const T*)noise, stochastic, key, tb);                                                    \
+  }
   switch (bits) {
     case 1: ACTNN_LAUNCH(1); break;
     case 2: ACTNN_LAUNCH(2); break;
@@ -212,10 +290,10 @@ template <typename T, typename ST>
 int launch_unpack(int bits, const int8_t* packed, const void* scale, const void* mn, void* out, int64_t N,
                   int64_t G, cudaStream_t s) {
   const int wpt = 8 / bits;
-  const int grid = grid_for(((N + wpt - 1) / wpt) * G);
+  const int64_t tasks = ((N + wpt - 1) / wpt) * G;
 #define ACTNN_LAUNCH(BITS)                                                                        \
-  unpack_single_kernel<T, ST, BITS><<<grid, kThreads, 0, s>>>(packed, (const ST*)scale, (const ST*)mn, \
-                                                              (T*)out, N, G)
+  unpack_single_kernel<T, ST, BITS><<<persistent_grid(unpack_single_kernel<T, ST, BITS>, kThreads, tasks), \
+                                      kThreads, 0, s>>>(packed, (const ST*)scale, (const ST*)mn, (T*)out, N, G)
   switch (bits) {
     case 1: ACTNN_LAUNCH(1); break;
     case 2: ACTNN_LAUNCH(2); break;

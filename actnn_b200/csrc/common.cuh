@@ -116,53 +116,56 @@ ACTNN_DEV uint32_t warp_transpose32(uint32_t x, const TransposePlan& p) {
 
 // ------------------------------------------------------------------ Philox4x32-10
 // Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3" (SC'11).
+// The ten round keys depend only on the seed, so the host expands them once and passes
+// them as kernel parameters: in the kernel they are constant-bank operands of the XORs
+// and the key schedule costs no instructions.
 struct Philox4 { uint32_t v[4]; };
+struct NoiseKey {
+  uint32_t k0[10], k1[10];   // round keys
+  uint32_t o0, o1;           // the 64-bit offset, upper half of the counter
+};
 
-ACTNN_HD void philox_mulhilo(uint32_t a, uint32_t b, uint32_t& hi, uint32_t& lo) {
-  const uint64_t p = (uint64_t)a * (uint64_t)b;
-  hi = (uint32_t)(p >> 32);
-  lo = (uint32_t)p;
+static inline NoiseKey make_noise_key(uint64_t seed, uint64_t offset) {
+  NoiseKey k;
+  uint32_t a = (uint32_t)seed, b = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    k.k0[r] = a; k.k1[r] = b;
+    a += 0x9E3779B9u; b += 0xBB67AE85u;
+  }
+  k.o0 = (uint32_t)offset; k.o1 = (uint32_t)(offset >> 32);
+  return k;
 }
-ACTNN_HD Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
-                               uint32_t k0, uint32_t k1) {
+
+#ifdef __CUDACC__
+ACTNN_DEV Philox4 noise_call(const NoiseKey& key, uint64_t c) {
+  uint32_t c0 = (uint32_t)c, c1 = (uint32_t)(c >> 32), c2 = key.o0, c3 = key.o1;
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
-    uint32_t hi0, lo0, hi1, lo1;
-    philox_mulhilo(0xD2511F53u, c0, hi0, lo0);
-    philox_mulhilo(0xCD9E8D57u, c2, hi1, lo1);
-    c0 = hi1 ^ c1 ^ k0;
-    c1 = lo1;
-    c2 = hi0 ^ c3 ^ k1;
-    c3 = lo0;
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    c0 = (uint32_t)(p1 >> 32) ^ c1 ^ key.k0[r];
+    c1 = (uint32_t)p1;
+    c2 = (uint32_t)(p0 >> 32) ^ c3 ^ key.k1[r];
+    c3 = (uint32_t)p0;
   }
   Philox4 o;
   o.v[0] = c0; o.v[1] = c1; o.v[2] = c2; o.v[3] = c3;
   return o;
 }
+#endif
 
 // Rounding-noise stream, indexed by position in the padded [N, G, 256] activation:
 // flat group q, position d in the group, lane t = d / 8, j = d % 8.
-//   counter = (lo32(c), hi32(c), lo32(offset), hi32(offset)), key = (lo32(seed), hi32(seed))
-//   16-bit activations: c = (q >> 1) * 32 + t; byte f = (q & 1) * 8 + j of the 128-bit
-//     output (little endian over v[0..3]) is k in [0, 255]; noise = (2k + 1 - 256) / 512.
-//     One call serves one lane for two neighbouring groups.
-//   float32 activations: c = q * 32 + t; 16-bit field j (v[j / 2] >> 16 * (j % 2)) is k;
-//     noise = (2k + 1 - 65536) / 131072.
+//   counter = (lo32(c), hi32(c), lo32(offset), hi32(offset)), key = (lo32(seed), hi32(seed));
+//   the call's four output words v[0..3] are extended to eight, e[i] = v[i] and
+//   e[4 + i] = v[i] ^ rotl32(v[(i + 1) % 4], 11) (see quant_math.cuh for why that is sound);
+//   16-bit activations: c = (q / 4) * 32 + t; byte j of the word pair (e[2h], e[2h + 1]),
+//     h = q % 4, is k in [0, 255]; noise = (2k + 1 - 256) / 512.
+//   float32 activations: c = (q / 2) * 32 + t; 16-bit field j of the words e[4h .. 4h + 3],
+//     h = q % 2, is k; noise = (2k + 1 - 65536) / 131072.
 // Both are odd multiples of the step, symmetric about zero, strictly inside (-0.5, 0.5)
 // and exactly representable in the activation dtype.  The resolution follows the dtype:
 // (x - min) * scale carries at most 11 (float16) or 8 (bfloat16) significant bits.
-struct NoiseKey { uint32_t k0, k1, o0, o1; };
-ACTNN_HD NoiseKey make_noise_key(uint64_t seed, uint64_t offset) {
-  NoiseKey k;
-  k.k0 = (uint32_t)seed; k.k1 = (uint32_t)(seed >> 32);
-  k.o0 = (uint32_t)offset; k.o1 = (uint32_t)(offset >> 32);
-  return k;
-}
-ACTNN_HD Philox4 noise_call(const NoiseKey& key, uint64_t c) {
-  return philox4x32_10((uint32_t)c, (uint32_t)(c >> 32), key.o0, key.o1, key.k0, key.k1);
-}
 
 // ------------------------------------------------------------------ host-side launch helpers
 struct DeviceInfo { int sm_count; };
@@ -170,5 +173,27 @@ const DeviceInfo& device_info();                   // api.cu (per current device
 int check_launch();                                // api.cu: cudaPeekAtLastError -> status
 
 static inline bool aligned(const void* p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+#ifdef __CUDACC__
+// Grid for a persistent warp-task kernel: as many blocks as can be resident at once
+// (SMs x blocks per SM), so that there is a single wave and no under-filled tail, but no
+// more than the tasks need.  The occupancy query is cached per kernel and device.
+template <typename Kernel>
+int persistent_grid(Kernel kernel, int threads, int64_t warp_tasks) {
+  static int per_sm[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (per_sm[dev] == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n <= 0) n = 1;
+    per_sm[dev] = n;
+  }
+  const int64_t resident = (int64_t)device_info().sm_count * per_sm[dev];
+  const int64_t needed = (warp_tasks + threads / 32 - 1) / (threads / 32);
+  const int64_t grid = needed < resident ? needed : resident;
+  return (int)(grid < 1 ? 1 : grid);
+}
+#endif
 
 }  // namespace actnn

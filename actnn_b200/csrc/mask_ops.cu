@@ -128,7 +128,7 @@ enum class Op { kReluFwd, kMaskBwd, kDropoutFwd };
 template <typename T, Op OP>
 __global__ void __launch_bounds__(kThreads)
 mask_kernel(const T* __restrict__ in, T* __restrict__ out, int32_t* __restrict__ mask, int64_t numel,
-            float inv, float p, const float* __restrict__ u, NoiseKey key) {
+            float inv, float p, const float* __restrict__ u, const NoiseKey key) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
@@ -195,7 +195,7 @@ mask_kernel(const T* __restrict__ in, T* __restrict__ out, int32_t* __restrict__
   }
 }
 
-__global__ void dropout_uniform_kernel(float* __restrict__ u, int64_t numel, NoiseKey key) {
+__global__ void dropout_uniform_kernel(float* __restrict__ u, int64_t numel, const NoiseKey key) {
   const int64_t oct = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (oct * 8 >= numel) return;
   const Philox4 r = noise_call(key, (uint64_t)oct);

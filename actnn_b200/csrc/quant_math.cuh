@@ -70,6 +70,39 @@ template <typename T> ACTNN_DEV GroupParams prepare_group(float mn, float mx, in
   return p;
 }
 
+// One lane prepares a group and ships (mn', scale) to the others: a single 32-bit shuffle
+// for 16-bit types (both values packed), two for float32.  QP<T> is the form the quantizer
+// consumes (values already duplicated into both halves for the packed types).
+template <typename T> struct QP { float mn1, scale; };
+template <> struct QP<__half> { __half2 mn2, sc2; };
+template <> struct QP<__nv_bfloat16> { __nv_bfloat162 mn2, sc2; };
+
+struct ParamWords { uint32_t w0, w1; };
+template <typename T> ACTNN_DEV ParamWords pack_params(const GroupParams& p) {
+  ParamWords w;
+  if constexpr (sizeof(T) == 4) {
+    w.w0 = __float_as_uint(p.mn1);
+    w.w1 = __float_as_uint(p.scale);
+  } else {
+    w.w0 = bits_of<T>(p.mn1) | (bits_of<T>(p.scale) << 16);
+    w.w1 = 0u;
+  }
+  return w;
+}
+template <typename T> ACTNN_DEV QP<T> fetch_params(const ParamWords& mine, int src_lane) {
+  QP<T> q;
+  if constexpr (sizeof(T) == 4) {
+    q.mn1 = __uint_as_float(__shfl_sync(kFull, mine.w0, src_lane));
+    q.scale = __uint_as_float(__shfl_sync(kFull, mine.w1, src_lane));
+  } else {
+    const uint32_t u = __shfl_sync(kFull, mine.w0, src_lane);
+    const uint32_t a = __byte_perm(u, u, 0x1010), b = __byte_perm(u, u, 0x3232);
+    q.mn2 = *reinterpret_cast<const decltype(q.mn2)*>(&a);
+    q.sc2 = *reinterpret_cast<const decltype(q.sc2)*>(&b);
+  }
+  return q;
+}
+
 // ------------------------------------------------------------------ octet min / max
 template <typename T> ACTNN_DEV void oct_minmax(const Oct<T>& o, float& mn, float& mx);
 template <> ACTNN_DEV void oct_minmax<float>(const Oct<float>& o, float& mn, float& mx) {
@@ -140,91 +173,144 @@ ACTNN_DEV Oct<float> noise_from_fields_f32(const Philox4& v) {
   return o;
 }
 
-// Noise for flat group q, this lane.  Keeps the last Philox call so that the two groups of
-// a pair (16-bit types) cost one call.
+// One Philox call yields four words; four more are derived as v[i] ^ rotl(v[i+1], 11).  Any
+// two of the eight words are jointly uniform (the derived word's partner enters only it and
+// its own original), hence any two of the 32 bytes are independent and uniform: second-order
+// statistics of the rounding noise equal those of independent noise at half the generator
+// cost.  A call thus serves one lane for four neighbouring groups (16-bit activations, one
+// byte per element) or two groups (float32, 16 bits per element).
+struct NoiseWords { uint32_t e[8]; };
+ACTNN_DEV NoiseWords expand_call(const Philox4& p) {
+  NoiseWords w;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    w.e[i] = p.v[i];
+    w.e[4 + i] = p.v[i] ^ __funnelshift_l(p.v[(i + 1) & 3], p.v[(i + 1) & 3], 11);
+  }
+  return w;
+}
+template <typename T> struct NoiseShape { static constexpr int GPC = sizeof(T) == 2 ? 4 : 2; };   // groups per call
+
+template <typename T> ACTNN_DEV Oct<T> noise_oct(const NoiseWords& w, int slot);
+template <> ACTNN_DEV Oct<float> noise_oct<float>(const NoiseWords& w, int slot) {
+  Philox4 v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v.v[i] = slot ? w.e[4 + i] : w.e[i];
+  return noise_from_fields_f32(v);
+}
+ACTNN_DEV void pick_pair(const NoiseWords& w, int slot, uint32_t& a, uint32_t& b) {
+  a = slot == 0 ? w.e[0] : slot == 1 ? w.e[2] : slot == 2 ? w.e[4] : w.e[6];
+  b = slot == 0 ? w.e[1] : slot == 1 ? w.e[3] : slot == 2 ? w.e[5] : w.e[7];
+}
+template <> ACTNN_DEV Oct<__half> noise_oct<__half>(const NoiseWords& w, int slot) {
+  uint32_t a, b;
+  pick_pair(w, slot, a, b);
+  return noise_from_bytes_f16(a, b);
+}
+template <> ACTNN_DEV Oct<__nv_bfloat16> noise_oct<__nv_bfloat16>(const NoiseWords& w, int slot) {
+  uint32_t a, b;
+  pick_pair(w, slot, a, b);
+  return noise_from_bytes_bf16(a, b);
+}
+
+// Noise for flat group q, this lane; keeps the last call (general path, any alignment).
 template <typename T> struct NoiseGen {
-  NoiseKey key;
+  static constexpr int GPC = NoiseShape<T>::GPC;
+  const NoiseKey key;                  // by value: the fields stay kernel-parameter (constant bank) reads
   uint64_t cached;
-  Philox4 ph;
+  NoiseWords w;
   int lane;
   ACTNN_DEV NoiseGen(const NoiseKey& k, int lane_) : key(k), cached(~0ull), lane(lane_) {}
-  ACTNN_DEV Oct<T> get(uint64_t q);
+  ACTNN_DEV Oct<T> get(uint64_t q) {
+    const uint64_t call = q / GPC;
+    if (call != cached) {
+      w = expand_call(noise_call(key, call * 32ull + (uint64_t)lane));
+      cached = call;
+    }
+    return noise_oct<T>(w, (int)(q % GPC));
+  }
 };
-template <> ACTNN_DEV Oct<float> NoiseGen<float>::get(uint64_t q) {
-  return noise_from_fields_f32(noise_call(key, q * 32ull + (uint64_t)lane));
-}
-template <> ACTNN_DEV Oct<__half> NoiseGen<__half>::get(uint64_t q) {
-  const uint64_t pair = q >> 1;
-  if (pair != cached) { ph = noise_call(key, pair * 32ull + (uint64_t)lane); cached = pair; }
-  return (q & 1) ? noise_from_bytes_f16(ph.v[2], ph.v[3]) : noise_from_bytes_f16(ph.v[0], ph.v[1]);
-}
-template <> ACTNN_DEV Oct<__nv_bfloat16> NoiseGen<__nv_bfloat16>::get(uint64_t q) {
-  const uint64_t pair = q >> 1;
-  if (pair != cached) { ph = noise_call(key, pair * 32ull + (uint64_t)lane); cached = pair; }
-  return (q & 1) ? noise_from_bytes_bf16(ph.v[2], ph.v[3]) : noise_from_bytes_bf16(ph.v[0], ph.v[1]);
+
+// The GPC octets of the aligned block of groups starting at q (q % GPC == 0), one call.
+template <typename T>
+ACTNN_DEV void noise_block(const NoiseKey& key, uint64_t q, int lane, Oct<T> (&out)[NoiseShape<T>::GPC]) {
+  const NoiseWords w = expand_call(noise_call(key, (q / NoiseShape<T>::GPC) * 32ull + (uint64_t)lane));
+#pragma unroll
+  for (int h = 0; h < NoiseShape<T>::GPC; ++h) out[h] = noise_oct<T>(w, h);
 }
 
 // ------------------------------------------------------------------ quantize one octet
-// Result: four registers, each holding two codes in the low bits of its 16-bit halves
-// (element 2m in the low half, 2m+1 in the high half).
-template <typename T>
-ACTNN_DEV void quantize_oct(const Oct<T>& x, const Oct<T>& nz, const GroupParams& p, int bits,
-                            uint32_t cp[4]);
+// The result stays in "magic" form: the registers still carry the exponent bits of the
+// rounding constant, code in the low mantissa bits.
+//   float16:            4 registers, two elements each: halves = 0x6600 + code
+//   float32 / bfloat16: 8 registers, one element each:  0x4B400000 + code
+// Because those high bits are the same for every element, shifted sums of magic registers
+// equal shifted sums of the codes plus a compile-time constant (mod 2^32): rows and bytes
+// are assembled with integer multiply-adds and one constant, without masking each code.
+template <typename T> struct Magic { uint32_t v[8]; };
+template <> struct Magic<__half> { uint32_t v[4]; };
+template <typename T> struct MagicInfo { static constexpr uint32_t bias = 0x4B400000u; static constexpr bool paired = false; };
+template <> struct MagicInfo<__half> { static constexpr uint32_t bias = 0x66006600u; static constexpr bool paired = true; };
 
-template <>
-ACTNN_DEV void quantize_oct<float>(const Oct<float>& x, const Oct<float>& nz, const GroupParams& p,
-                                   int bits, uint32_t cp[4]) {
-  const float B = (float)((1 << bits) - 1);
-  uint32_t c[8];
+// CLAMP_LOW = false may be used when min really is the group minimum: then
+// (x - mn') * scale + noise >= -0.5 always and the round-to-even of the magic add maps it
+// to code 0 on its own.
+template <typename T, bool CLAMP_LOW, int BITS>
+ACTNN_DEV Magic<T> quantize_oct(const Oct<T>& x, const Oct<T>& nz, const QP<T>& p) {
+  Magic<T> m;
+  if constexpr (sizeof(T) == 4) {
+    constexpr float B = (float)((1 << BITS) - 1);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float t = __fmul_rn(__fsub_rn(x.f[j], p.mn1), p.scale);
-    t = __fadd_rn(t, nz.f[j]);
-    t = fminf(fmaxf(t, 0.f), B);                            // NaN -> 0
-    c[j] = __float_as_uint(__fadd_rn(t, 12582912.f)) & 0x1ffu;
+    for (int j = 0; j < 8; ++j) {
+      float t = __fmul_rn(__fsub_rn(x.f[j], p.mn1), p.scale);
+      t = __fadd_rn(t, nz.f[j]);
+      if (CLAMP_LOW) t = fmaxf(t, 0.f);
+      t = fminf(t, B);                                      // NaN -> B
+      m.v[j] = __float_as_uint(__fadd_rn(t, 12582912.f));
+    }
+  } else if constexpr (DType<T>::id == ACTNN_F16) {
+    // (2^BITS - 1) and 1536 as half2 bit patterns; 1536 = 0x6600: every t in [-0.5, 255.5]
+    // lands in [1024, 2048), where the spacing is 1
+    constexpr uint32_t kB[9] = {0, 0x3C003C00u, 0x42004200u, 0x47004700u, 0x4B804B80u, 0x4FC04FC0u,
+                                0x53E053E0u, 0x57F057F0u, 0x5BF85BF8u};
+    const uint32_t b_bits = kB[BITS], magic_bits = 0x66006600u, zero_bits = 0u;
+    const __half2 B2 = *reinterpret_cast<const __half2*>(&b_bits);
+    const __half2 magic2 = *reinterpret_cast<const __half2*>(&magic_bits);
+    const __half2 zero2 = *reinterpret_cast<const __half2*>(&zero_bits);
+    const __half2* xv = reinterpret_cast<const __half2*>(x.r);
+    const __half2* nv = reinterpret_cast<const __half2*>(nz.r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __half2 t = __hmul2_rn(__hsub2_rn(xv[k], p.mn2), p.sc2);
+      t = __hadd2_rn(t, nv[k]);
+      if (CLAMP_LOW) t = __hmax2(t, zero2);
+      t = __hmin2(t, B2);                                   // NaN -> B
+      t = __hadd2_rn(t, magic2);
+      m.v[k] = *reinterpret_cast<const uint32_t*>(&t);
+    }
+  } else {
+    // bfloat16 patterns of 2^BITS - 1
+    constexpr uint32_t kB[9] = {0, 0x3F803F80u, 0x40404040u, 0x40E040E0u, 0x41704170u, 0x41F841F8u,
+                                0x427C427Cu, 0x42FE42FEu, 0x437F437Fu};
+    const uint32_t b_bits = kB[BITS], zero_bits = 0u;
+    const __nv_bfloat162 B2 = *reinterpret_cast<const __nv_bfloat162*>(&b_bits);
+    const __nv_bfloat162 zero2 = *reinterpret_cast<const __nv_bfloat162*>(&zero_bits);
+    const __nv_bfloat162* xv = reinterpret_cast<const __nv_bfloat162*>(x.r);
+    const __nv_bfloat162* nv = reinterpret_cast<const __nv_bfloat162*>(nz.r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __nv_bfloat162 t = __hmul2_rn(__hsub2_rn(xv[k], p.mn2), p.sc2);
+      t = __hadd2_rn(t, nv[k]);
+      if (CLAMP_LOW) t = __hmax2(t, zero2);
+      t = __hmin2(t, B2);                                   // NaN -> B
+      const uint32_t u = *reinterpret_cast<const uint32_t*>(&t);
+      // bfloat16 -> float32 is a shift; 8 mantissa bits cannot hold 255 plus a round bit, so
+      // the integer rounding runs in float32 (1.5 * 2^23 also absorbs t in [-0.5, 0))
+      m.v[2 * k] = __float_as_uint(__fadd_rn(__uint_as_float(u << 16), 12582912.f));
+      m.v[2 * k + 1] = __float_as_uint(__fadd_rn(__uint_as_float(u & 0xffff0000u), 12582912.f));
+    }
   }
-#pragma unroll
-  for (int m = 0; m < 4; ++m) cp[m] = c[2 * m] | (c[2 * m + 1] << 16);
-}
-
-template <>
-ACTNN_DEV void quantize_oct<__half>(const Oct<__half>& x, const Oct<__half>& nz, const GroupParams& p,
-                                    int bits, uint32_t cp[4]) {
-  const __half2 mn2 = __float2half2_rn(p.mn1), sc2 = __float2half2_rn(p.scale);
-  const __half2 B2 = __float2half2_rn((float)((1 << bits) - 1));
-  const __half2 zero2 = __float2half2_rn(0.f), magic2 = __float2half2_rn(1024.f);
-  const __half2* xv = reinterpret_cast<const __half2*>(x.r);
-  const __half2* nv = reinterpret_cast<const __half2*>(nz.r);
-#pragma unroll
-  for (int m = 0; m < 4; ++m) {
-    __half2 t = __hmul2_rn(__hsub2_rn(xv[m], mn2), sc2);
-    t = __hadd2_rn(t, nv[m]);
-    t = __hmin2(__hmax2(t, zero2), B2);                     // NaN -> 0
-    t = __hadd2_rn(t, magic2);
-    cp[m] = *reinterpret_cast<const uint32_t*>(&t) & 0x03ff03ffu;
-  }
-}
-
-template <>
-ACTNN_DEV void quantize_oct<__nv_bfloat16>(const Oct<__nv_bfloat16>& x, const Oct<__nv_bfloat16>& nz,
-                                           const GroupParams& p, int bits, uint32_t cp[4]) {
-  const __nv_bfloat162 mn2 = __float2bfloat162_rn(p.mn1), sc2 = __float2bfloat162_rn(p.scale);
-  const __nv_bfloat162 B2 = __float2bfloat162_rn((float)((1 << bits) - 1));
-  const __nv_bfloat162 zero2 = __float2bfloat162_rn(0.f);
-  const __nv_bfloat162* xv = reinterpret_cast<const __nv_bfloat162*>(x.r);
-  const __nv_bfloat162* nv = reinterpret_cast<const __nv_bfloat162*>(nz.r);
-#pragma unroll
-  for (int m = 0; m < 4; ++m) {
-    __nv_bfloat162 t = __hmul2_rn(__hsub2_rn(xv[m], mn2), sc2);
-    t = __hadd2_rn(t, nv[m]);
-    t = __hmin2(__hmax2(t, zero2), B2);                     // NaN -> 0
-    const uint32_t u = *reinterpret_cast<const uint32_t*>(&t);
-    // bfloat16 -> float32 is a shift; 8 mantissa bits cannot hold 255 + a round bit, so the
-    // integer rounding runs in float32
-    const uint32_t lo = __float_as_uint(__fadd_rn(__uint_as_float(u << 16), 12582912.f)) & 0x1ffu;
-    const uint32_t hi = __float_as_uint(__fadd_rn(__uint_as_float(u & 0xffff0000u), 12582912.f)) & 0x1ffu;
-    cp[m] = lo | (hi << 16);
-  }
+  return m;
 }
 
 // ------------------------------------------------------------------ dequantize
@@ -245,19 +331,84 @@ template <int OFF, int NB> ACTNN_DEV uint32_t get_bits(const uint32_t* S) {
   constexpr int w = OFF / 32, s = OFF % 32;
   uint32_t v = S[w] >> s;
   if constexpr (s + NB > 32) v |= S[w + 1] << (32 - s);
-  return v & ((1u << NB) - 1u);
+  if constexpr (NB >= 32) return v;
+  else return v & ((1u << NB) - 1u);
 }
 
-// Append the eight B-bit codes of one octet at bit offset OFF: code j at OFF + j*B.
-template <int B, int OFF> ACTNN_DEV void put_codes(uint32_t* S, const uint32_t cp[4]) {
-  const uint32_t p0 = (cp[0] | (cp[0] >> (16 - B))) & ((1u << (2 * B)) - 1u);
-  const uint32_t p1 = (cp[1] | (cp[1] >> (16 - B))) & ((1u << (2 * B)) - 1u);
-  const uint32_t p2 = (cp[2] | (cp[2] >> (16 - B))) & ((1u << (2 * B)) - 1u);
-  const uint32_t p3 = (cp[3] | (cp[3] >> (16 - B))) & ((1u << (2 * B)) - 1u);
-  put_bits<OFF + 0 * B, 2 * B>(S, p0);
-  put_bits<OFF + 2 * B, 2 * B>(S, p1);
-  put_bits<OFF + 4 * B, 2 * B>(S, p2);
-  put_bits<OFF + 6 * B, 2 * B>(S, p3);
+// sum over k of (c << (step * k)) mod 2^32, evaluated at compile time
+constexpr uint32_t shifted_sum(uint32_t c, int step, int count) {
+  uint32_t acc = 0;
+  for (int k = 0; k < count; ++k) acc += (step * k < 32) ? (c << (step * k)) : 0u;
+  return acc;
+}
+
+// The lane's row for one octet: eight B-bit codes laid end to end, code j at bit B*j.
+// lo = bits 0..31, hi = bits 32..63 (only B > 4 reaches hi).
+template <typename T, int B> ACTNN_DEV void row_from_magic(const Magic<T>& m, uint32_t& lo, uint32_t& hi) {
+  hi = 0u;
+  if constexpr (MagicInfo<T>::paired) {
+    constexpr uint32_t bias = MagicInfo<T>::bias;
+    if constexpr (B <= 2) {
+      // even elements accumulate in the low half, odd ones in the high half
+      uint32_t acc = m.v[0] + (m.v[1] << (2 * B)) + (m.v[2] << (4 * B)) + (m.v[3] << (6 * B));
+      acc -= shifted_sum(bias, 2 * B, 4);
+      lo = (acc | (acc >> (16 - B))) & ((1u << (8 * B)) - 1u);
+    } else if constexpr (B <= 4) {
+      uint32_t a = m.v[0] + (m.v[1] << (2 * B)) - shifted_sum(bias, 2 * B, 2);
+      uint32_t b = m.v[2] + (m.v[3] << (2 * B)) - shifted_sum(bias, 2 * B, 2);
+      a = (a | (a >> (16 - B))) & ((1u << (4 * B)) - 1u);
+      b = (b | (b >> (16 - B))) & ((1u << (4 * B)) - 1u);
+      lo = a | (b << (4 * B));
+    } else {
+      uint32_t S[2] = {0u, 0u};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t c = m.v[k] & 0x01ff01ffu;
+        const uint32_t pr = (c | (c >> (16 - B))) & ((1u << (2 * B)) - 1u);
+        if (k == 0) put_bits<0 * B, 2 * B>(S, pr);
+        if (k == 1) put_bits<2 * B, 2 * B>(S, pr);
+        if (k == 2) put_bits<4 * B, 2 * B>(S, pr);
+        if (k == 3) put_bits<6 * B, 2 * B>(S, pr);
+      }
+      lo = S[0]; hi = S[1];
+    }
+  } else {
+    constexpr uint32_t bias = MagicInfo<T>::bias;
+    if constexpr (B <= 4) {
+      uint32_t acc = m.v[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) acc += m.v[j] << (B * j);
+      lo = acc - shifted_sum(bias, B, 8);
+    } else if constexpr (B == 8) {
+      lo = (m.v[0] + (m.v[1] << 8) + (m.v[2] << 16) + (m.v[3] << 24)) - shifted_sum(bias, 8, 4);
+      hi = (m.v[4] + (m.v[5] << 8) + (m.v[6] << 16) + (m.v[7] << 24)) - shifted_sum(bias, 8, 4);
+    } else {
+      uint32_t S[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t c = m.v[j] & 0x1ffu;
+        if (j == 0) put_bits<0 * B, B>(S, c);
+        if (j == 1) put_bits<1 * B, B>(S, c);
+        if (j == 2) put_bits<2 * B, B>(S, c);
+        if (j == 3) put_bits<3 * B, B>(S, c);
+        if (j == 4) put_bits<4 * B, B>(S, c);
+        if (j == 5) put_bits<5 * B, B>(S, c);
+        if (j == 6) put_bits<6 * B, B>(S, c);
+        if (j == 7) put_bits<7 * B, B>(S, c);
+      }
+      lo = S[0]; hi = S[1];
+    }
+  }
+}
+
+// Place a row (8B bits) at bit offset OFF of the bundle string S.
+template <int B, int OFF> ACTNN_DEV void put_row(uint32_t* S, uint32_t lo, uint32_t hi) {
+  if constexpr (8 * B <= 32) {
+    put_bits<OFF, 8 * B>(S, lo);
+  } else {
+    put_bits<OFF, 32>(S, lo);
+    put_bits<OFF + 32, 8 * B - 32>(S, hi);
+  }
 }
 
 // The eight B-bit codes stored at bit offset OFF.

@@ -502,29 +502,36 @@ def _philox_calls(count: int, seed: int, offset: int) -> np.ndarray:
     return philox4x32_10(ctr, (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
 
 
+def _expand_call(r: np.ndarray) -> np.ndarray:
+    """Eight words per call: the four outputs and ``v[i] ^ rotl32(v[(i + 1) % 4], 11)``."""
+    nxt = np.roll(r, -1, axis=1)
+    rot = ((nxt << np.uint32(11)) | (nxt >> np.uint32(21))).astype(np.uint32)
+    return np.concatenate([r, r ^ rot], axis=1)
+
+
 def philox_noise(numel: int, dtype: torch.dtype, seed: int, offset: int) -> torch.Tensor:
     """The rounding noise the CUDA pack kernels draw when no noise tensor is injected.
 
     Element ``e`` of the padded ``[N, G, 256]`` activation: flat group ``q = e // 256``,
-    position ``d = e % 256``, lane ``t = d // 8``, ``j = d % 8``.
-    * float16 / bfloat16: call ``c = (q >> 1) * 32 + t``; byte ``f = (q & 1) * 8 + j`` of the
-      128-bit output (little endian over the four words) is ``k``; noise ``(2k + 1 - 256) / 512``.
-    * float32: call ``c = q * 32 + t``; 16-bit field ``j`` (word ``j // 2``, half ``j % 2``) is
-      ``k``; noise ``(2k + 1 - 65536) / 131072``.
+    position ``d = e % 256``, lane ``t = d // 8``, ``j = d % 8``.  Each call's four output
+    words are extended to eight (``_expand_call``).
+    * float16 / bfloat16: call ``c = (q // 4) * 32 + t``; with ``h = q % 4``, byte ``j`` of the
+      word pair ``(e[2h], e[2h + 1])`` is ``k``; noise ``(2k + 1 - 256) / 512``.
+    * float32: call ``c = (q // 2) * 32 + t``; with ``h = q % 2``, 16-bit field ``j`` of the
+      words ``e[4h .. 4h + 3]`` is ``k``; noise ``(2k + 1 - 65536) / 131072``.
     """
     e = np.arange(numel, dtype=np.int64)
     q, d = e // 256, e % 256
     t, j = d // 8, d % 8
     if dtype == torch.float32:
-        c = q * 32 + t
-        r = _philox_calls(int(c.max()) + 1 if numel else 0, seed, offset)
-        k = (r[c, j // 2] >> (16 * (j % 2)).astype(np.uint32)) & np.uint32(0xFFFF)
+        c, h = (q // 2) * 32 + t, q % 2
+        w = _expand_call(_philox_calls(int(c.max()) + 1 if numel else 0, seed, offset))
+        k = (w[c, 4 * h + j // 2] >> (16 * (j % 2)).astype(np.uint32)) & np.uint32(0xFFFF)
         u = (2.0 * k.astype(np.float64) + 1 - 65536) / 131072
     else:
-        c = (q >> 1) * 32 + t
-        f = (q & 1) * 8 + j
-        r = _philox_calls(int(c.max()) + 1 if numel else 0, seed, offset)
-        k = (r[c, f // 4] >> (8 * (f % 4)).astype(np.uint32)) & np.uint32(0xFF)
+        c, h = (q // 4) * 32 + t, q % 4
+        w = _expand_call(_philox_calls(int(c.max()) + 1 if numel else 0, seed, offset))
+        k = (w[c, 2 * h + j // 4] >> (8 * (j % 4)).astype(np.uint32)) & np.uint32(0xFF)
         u = (2.0 * k.astype(np.float64) + 1 - 256) / 512
     return torch.from_numpy(u.astype(np.float32)).to(dtype)
 
