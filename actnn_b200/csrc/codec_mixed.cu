@@ -163,38 +163,23 @@ template <int B> ACTNN_DEV uint32_t spread_codes_to_bytes(uint32_t r) {   // fou
   }
 }
 
-template <typename T, typename ST, int B>
-ACTNN_DEV void unpack_bundle(const int32_t* __restrict__ in, const BundleCoord& c,
-                             const ST* __restrict__ scale, const ST* __restrict__ mn, T* __restrict__ out,
-                             const TransposePlan& plan, int lane) {
+// `words[k]` is word 32k + lane of the bundle (zero past its end); lanes 0..count-1 hold the
+// statistics of their group in (stat_scale, stat_mn).  Both were loaded ahead of time.
+template <typename T, int B>
+ACTNN_DEV void unpack_bundle(const uint32_t (&words)[8], float stat_scale, float stat_mn, const BundleCoord& c,
+                             T* __restrict__ out, const TransposePlan& plan, int lane) {
   constexpr int E = 1 << (B < 6 ? B : 5);              // table entries per group
   constexpr int GPC = (32 / E) < kBundle ? (32 / E) : kBundle;   // groups served by one table computation
-  const int words = c.count * 8 * B;
   uint32_t S[B];
 #pragma unroll
-  for (int k = 0; k < B; ++k) {
-    const int o = k * 32 + lane;
-    const uint32_t w = o < words ? (uint32_t)__ldg(in + o) : 0u;
-    S[k] = warp_transpose32(w, plan);
-  }
-  float stat_scale = 1.f, stat_mn = 0.f;               // B >= 6: lane l holds the statistics of group l
-  if constexpr (B >= 6) {
-    if (lane < c.count) {
-      stat_scale = load_scalar<ST>(scale, c.q0 + lane);
-      stat_mn = load_scalar<ST>(mn, c.q0 + lane);
-    }
-  }
+  for (int k = 0; k < B; ++k) S[k] = warp_transpose32(words[k], plan);
   uint32_t entry = 0u, pairs = 0u;
 #pragma unroll
   for (int gi = 0; gi < kBundle; ++gi) {
     if constexpr (B < 6) {
       if (gi % GPC == 0) {                               // (re)build the table for groups gi .. gi+GPC-1
-        const int g = gi + lane / E;
-        float sc = 1.f, m = 0.f;
-        if (lane < GPC * E && g < c.count) {
-          sc = load_scalar<ST>(scale, c.q0 + g);
-          m = load_scalar<ST>(mn, c.q0 + g);
-        }
+        const int g = (gi + lane / E) & (kBundle - 1);
+        const float sc = __shfl_sync(kFull, stat_scale, g), m = __shfl_sync(kFull, stat_mn, g);
         entry = dequant_bits<T>((float)(lane % E), sc, m);
         if constexpr (sizeof(T) == 2 && B <= 2)
           pairs = entry | (__shfl_down_sync(kFull, entry, 1) << 16);
@@ -254,20 +239,52 @@ unpack_mixed_kernel(const int32_t* __restrict__ packed, const int32_t* __restric
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const TransposePlan plan = make_transpose_plan(lane);
 
-  for (BundleWalker walk(warp, nwarps, N, G); walk.valid(); walk.next()) {
-    const BundleCoord c = walk.coord();
-    const int b = __ldg(bits + c.n);
-    const int32_t* in = packed + __ldg(word_offsets + c.n) + (int64_t)c.g0 * 8 * b;
-    switch (b) {
-      case 1: unpack_bundle<T, ST, 1>(in, c, scale, mn, out, plan, lane); break;
-      case 2: unpack_bundle<T, ST, 2>(in, c, scale, mn, out, plan, lane); break;
-      case 3: unpack_bundle<T, ST, 3>(in, c, scale, mn, out, plan, lane); break;
-      case 4: unpack_bundle<T, ST, 4>(in, c, scale, mn, out, plan, lane); break;
-      case 5: unpack_bundle<T, ST, 5>(in, c, scale, mn, out, plan, lane); break;
-      case 6: unpack_bundle<T, ST, 6>(in, c, scale, mn, out, plan, lane); break;
-      case 7: unpack_bundle<T, ST, 7>(in, c, scale, mn, out, plan, lane); break;
-      case 8: unpack_bundle<T, ST, 8>(in, c, scale, mn, out, plan, lane); break;
-      default: break;
+  // A bundle's input is only b * 128 bytes per warp: issue the loads of DEPTH bundles before
+  // decoding the first, so that enough bytes are in flight to cover the memory latency.
+  constexpr int DEPTH = 2;
+  BundleWalker walk(warp, nwarps, N, G);
+  while (walk.valid()) {
+    BundleCoord t_c[DEPTH];
+    int t_b[DEPTH];
+    bool t_ok[DEPTH];
+    uint32_t t_w[DEPTH][8];
+    float t_sc[DEPTH], t_m[DEPTH];
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      t_ok[d] = walk.valid();
+      t_b[d] = 0;
+      t_sc[d] = 1.f;
+      t_m[d] = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t_w[d][k] = 0u;
+      if (t_ok[d]) {
+        t_c[d] = walk.coord();
+        const BundleCoord& c = t_c[d];
+        const int b = __ldg(bits + c.n);
+        t_b[d] = b;
+        const int32_t* in = packed + (__ldg(word_offsets + c.n) + (int64_t)c.g0 * 8 * b);
+        const int words = c.count * 8 * b;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (k < b && k * 32 + lane < words) t_w[d][k] = (uint32_t)__ldg(in + k * 32 + lane);
+        if (lane < c.count) {
+          t_sc[d] = load_scalar<ST>(scale, c.q0 + lane);
+          t_m[d] = load_scalar<ST>(mn, c.q0 + lane);
+        }
+        walk.next();
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (!t_ok[d]) break;                                // warp-uniform
+#define ACTNN_CASE(B) \
+      case B: unpack_bundle<T, B>(t_w[d], t_sc[d], t_m[d], t_c[d], out, plan, lane); break;
+      switch (t_b[d]) {
+        ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
+        ACTNN_CASE(8)
+        default: break;
+      }
+#undef ACTNN_CASE
     }
   }
 }

@@ -193,56 +193,80 @@ unpack_single_kernel(const int8_t* __restrict__ packed, const ST* __restrict__ s
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const int64_t nblocks = (N + WPT - 1) / WPT;
 
-  for (PairWalker walk(warp, nwarps, nblocks, G); walk.valid(); walk.next()) {
-    const int64_t no = walk.no;
-    const int64_t g = walk.r;
-    const uint2 w = __ldg(reinterpret_cast<const uint2*>(packed + ((no * G + g) * kGroup + lane * kOct)));
-    // lane l serves sample no*wpt + l / E (TABLE) or sample no*wpt + l (BITS == 8)
-    const int my_s = TABLE ? lane / E : lane;
-    const int64_t my_n = no * WPT + my_s;
-    float sc = 1.f, m = 0.f;
-    if (my_s < WPT && my_n < N) {
-      sc = load_scalar<ST>(scale, my_n * G + g);
-      m = load_scalar<ST>(mn, my_n * G + g);
-    }
-    uint32_t entry = 0u, pairs = 0u;
-    if constexpr (TABLE) {
-      entry = dequant_bits<T>((float)(lane % E), sc, m);
-      if constexpr (sizeof(T) == 2 && BITS <= 2) pairs = entry | (__shfl_down_sync(kFull, entry, 1) << 16);
-    }
+  // The packed stream is an eighth of the output or less, so a task's loads are small; to
+  // keep enough bytes in flight each warp issues the loads of DEPTH tasks before it decodes
+  // the first of them.
+  constexpr int DEPTH = 2;
+  const int my_s = TABLE ? lane / E : lane;                // lane l serves sample no*wpt + my_s
+  PairWalker walk(warp, nwarps, nblocks, G);
+  while (walk.valid()) {
+    int64_t t_no[DEPTH], t_g[DEPTH];
+    uint2 t_w[DEPTH];
+    float t_sc[DEPTH], t_m[DEPTH];
+    bool t_ok[DEPTH];
 #pragma unroll
-    for (int ni = 0; ni < WPT; ++ni) {
-      const int64_t n = no * WPT + ni;
-      Oct<T> o;
-      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-      if constexpr (sizeof(T) == 2 && BITS <= 2) {
-        const uint32_t t01 = __shfl_sync(kFull, pairs, ni * E);
-        const uint32_t t23 = BITS == 2 ? __shfl_sync(kFull, pairs, ni * E + 2) : t01;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint32_t y = ((h ? w.y : w.x) >> (ni * BITS)) & (0x01010101u * (uint32_t)(E - 1));
-          const uint32_t sel = y * 0x22u + 0x10101010u;
-          ow[2 * h] = __byte_perm(t01, t23, sel);
-          ow[2 * h + 1] = __byte_perm(t01, t23, sel >> 16);
+    for (int d = 0; d < DEPTH; ++d) {
+      t_ok[d] = walk.valid();
+      t_no[d] = walk.no;
+      t_g[d] = walk.r;
+      t_w[d] = make_uint2(0u, 0u);
+      t_sc[d] = 1.f;
+      t_m[d] = 0.f;
+      if (t_ok[d]) {
+        t_w[d] = __ldg(reinterpret_cast<const uint2*>(packed + ((t_no[d] * G + t_g[d]) * kGroup + lane * kOct)));
+        const int64_t my_n = t_no[d] * WPT + my_s;
+        if (my_s < WPT && my_n < N) {
+          t_sc[d] = load_scalar<ST>(scale, my_n * G + t_g[d]);
+          t_m[d] = load_scalar<ST>(mn, my_n * G + t_g[d]);
         }
-      } else {
-        uint32_t v[8];
-        const float sc_n = TABLE ? 0.f : __shfl_sync(kFull, sc, ni), m_n = TABLE ? 0.f : __shfl_sync(kFull, m, ni);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t code = ((((j < 4) ? w.x : w.y) >> (8 * (j & 3))) >> (ni * BITS)) & (uint32_t)(E - 1);
-          if constexpr (TABLE) v[j] = __shfl_sync(kFull, entry, ni * E + (int)code);
-          else v[j] = dequant_bits<T>((float)code, sc_n, m_n);
-        }
-        if constexpr (sizeof(T) == 4) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ow[j] = v[j];
-        } else {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) ow[k] = v[2 * k] | (v[2 * k + 1] << 16);
-        }
+        walk.next();
       }
-      if (n < N) store_oct<T>(out + (n * G + g) * kGroup + lane * kOct, o);
+    }
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (!t_ok[d]) break;                                 // warp-uniform
+      const int64_t no = t_no[d], g = t_g[d];
+      const uint2 w = t_w[d];
+      const float sc = t_sc[d], m = t_m[d];
+      uint32_t entry = 0u, pairs = 0u;
+      if constexpr (TABLE) {
+        entry = dequant_bits<T>((float)(lane % E), sc, m);
+        if constexpr (sizeof(T) == 2 && BITS <= 2) pairs = entry | (__shfl_down_sync(kFull, entry, 1) << 16);
+      }
+#pragma unroll
+      for (int ni = 0; ni < WPT; ++ni) {
+        const int64_t n = no * WPT + ni;
+        Oct<T> o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+        if constexpr (sizeof(T) == 2 && BITS <= 2) {
+          const uint32_t t01 = __shfl_sync(kFull, pairs, ni * E);
+          const uint32_t t23 = BITS == 2 ? __shfl_sync(kFull, pairs, ni * E + 2) : t01;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t y = ((h ? w.y : w.x) >> (ni * BITS)) & (0x01010101u * (uint32_t)(E - 1));
+            const uint32_t sel = y * 0x22u + 0x10101010u;
+            ow[2 * h] = __byte_perm(t01, t23, sel);
+            ow[2 * h + 1] = __byte_perm(t01, t23, sel >> 16);
+          }
+        } else {
+          uint32_t v[8];
+          const float sc_n = TABLE ? 0.f : __shfl_sync(kFull, sc, ni), m_n = TABLE ? 0.f : __shfl_sync(kFull, m, ni);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t code = ((((j < 4) ? w.x : w.y) >> (8 * (j & 3))) >> (ni * BITS)) & (uint32_t)(E - 1);
+            if constexpr (TABLE) v[j] = __shfl_sync(kFull, entry, ni * E + (int)code);
+            else v[j] = dequant_bits<T>((float)code, sc_n, m_n);
+          }
+          if constexpr (sizeof(T) == 4) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ow[j] = v[j];
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ow[k] = v[2 * k] | (v[2 * k + 1] << 16);
+          }
+        }
+        if (n < N) store_oct<T>(out + (n * G + g) * kGroup + lane * kOct, o);
+      }
     }
   }
 }

@@ -139,8 +139,11 @@ static inline NoiseKey make_noise_key(uint64_t seed, uint64_t offset) {
 #ifdef __CUDACC__
 ACTNN_DEV Philox4 noise_call(const NoiseKey& key, uint64_t c) {
   uint32_t c0 = (uint32_t)c, c1 = (uint32_t)(c >> 32), c2 = key.o0, c3 = key.o1;
+#ifndef ACTNN_PHILOX_ROUNDS
+#define ACTNN_PHILOX_ROUNDS 10
+#endif
 #pragma unroll
-  for (int r = 0; r < 10; ++r) {
+  for (int r = 0; r < ACTNN_PHILOX_ROUNDS; ++r) {
     const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
     const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
     c0 = (uint32_t)(p1 >> 32) ^ c1 ^ key.k0[r];
