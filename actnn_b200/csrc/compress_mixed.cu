@@ -1,0 +1,43 @@
+// The whole adaptive (per-sample bit width) compress of one activation behind one call:
+// per-group min/max -> per-sample sensitivity -> greedy bit allocation -> scale, stochastic
+// rounding and mixed-precision pack.  Four kernel launches on the caller's stream, no host
+// synchronisation, no allocation: the per-group min / max that only live between the first
+// and the last kernel go to a workspace the caller provides.
+#include "quant_math.cuh"
+
+using namespace actnn;
+
+extern "C" int64_t actnn_compress_mixed_workspace(int64_t N, int64_t G, int dtype) {
+  if (N < 0 || G < 0 || dtype < ACTNN_F32 || dtype > ACTNN_BF16) return -1;
+  // min and max of every group in the activation dtype, each rounded up to 256 bytes
+  const int64_t one = (N * G * dtype_size(dtype) + 255) / 256 * 256;
+  return 2 * one;
+}
+
+extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* scale, void* mn_out,
+                                    int32_t* bits_out, int64_t* word_offsets_out, float* C_out, void* workspace,
+                                    int64_t workspace_bytes, int64_t N, int64_t G, int64_t group_size, int dtype,
+                                    int stat_dtype, float range_factor, float coeff, const float* grad_scale,
+                                    int initial_bits, double target, int stochastic, const void* noise,
+                                    uint64_t seed, uint64_t offset, actnn_stream_t stream) {
+  if (N < 0 || G < 0 || group_size != kGroup) return ACTNN_ERR_SHAPE;
+  if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
+  if (initial_bits < 2 || initial_bits > 8) return ACTNN_ERR_BITS;
+  if (N == 0 || G == 0) return ACTNN_OK;
+  if (!data || !packed || !scale || !mn_out || !bits_out || !word_offsets_out || !C_out || !workspace)
+    return ACTNN_ERR_NULL;
+  const int64_t need = actnn_compress_mixed_workspace(N, G, dtype);
+  if (workspace_bytes < need) return ACTNN_ERR_CAPACITY;
+  if (!aligned(workspace, 256)) return ACTNN_ERR_ALIGN;
+  void* mn = workspace;
+  void* mx = (char*)workspace + need / 2;
+  int st = actnn_minimax(data, mn, mx, N * G, group_size, dtype, stream);
+  if (st) return st;
+  st = actnn_range_sqr(mn, mx, N, G, dtype, range_factor, coeff, grad_scale, C_out, stream);
+  if (st) return st;
+  st = actnn_calc_precision(C_out, nullptr, N, initial_bits, target, bits_out, word_offsets_out, G, group_size,
+                            stream);
+  if (st) return st;
+  return actnn_pack_mixed(data, mn, mx, bits_out, word_offsets_out, packed, scale, mn_out, N, G, group_size, dtype,
+                          stat_dtype, stochastic, noise, seed, offset, stream);
+}

@@ -27,7 +27,7 @@ from .conf import config
 from .cpp_extension import backward_func as ext_backward_func
 from .cpp_extension import minimax as ext_minimax
 from .cpp_extension import quantization as ext_quantization
-from .qscheme import group_minimax
+from .qscheme import group_minimax, to_groups
 from .utils import compute_tensor_bytes, empty_cache, get_memory_usage, swap_to_cpu
 
 QParams = namedtuple("QParams", ["range", "zero_point", "num_bits"])
@@ -95,16 +95,6 @@ def no_scheme_compute_quantization_bits(input):
     return groups, config.activation_compression_bits[0], mn, mx
 
 
-def _to_groups(input):
-    N = input.shape[0]
-    gs = config.group_size
-    flat = input.view(N, -1)
-    f = flat.shape[1]
-    if f % gs != 0:
-        flat = torch.cat([flat, torch.zeros([N, (f // gs + 1) * gs - f], dtype=input.dtype, device=input.device)], 1)
-    return flat.view(N, -1, gs)
-
-
 def quantize_activation(input, scheme):
     """Compress one activation; returns ``(q_input, q_bits, q_scale, q_min)`` (ops.py:99-118)."""
     if not config.compress_activation:
@@ -122,16 +112,20 @@ def quantize_activation(input, scheme):
         return q_input, q_bits, q_scale.to(stat_dtype), q_min.to(stat_dtype)
 
     if scheme:
-        groups, q_bits, mn, mx = scheme.compute_quantization_bits(input)
-        q_input, q_scale, q_min = ext_quantization.pack_mixed_precision(
-            groups, mn, mx, q_bits, config.stochastic, word_offsets=getattr(q_bits, "word_offsets", None),
-            total_bits=getattr(q_bits, "total_bits", None), stat_dtype=stat_dtype, return_min=True)
+        fused = scheme.compress(input, stat_dtype) if hasattr(scheme, "compress") else None
+        if fused is not None:
+            q_input, q_bits, q_scale, q_min = fused
+        else:
+            groups, q_bits, mn, mx = scheme.compute_quantization_bits(input)
+            q_input, q_scale, q_min = ext_quantization.pack_mixed_precision(
+                groups, mn, mx, q_bits, config.stochastic, word_offsets=getattr(q_bits, "word_offsets", None),
+                total_bits=getattr(q_bits, "total_bits", None), stat_dtype=stat_dtype, return_min=True)
     else:
         q_bits = config.activation_compression_bits[0]
         if config.pergroup:
             # one pass over the activation: min/max, rounding and packing fused
             q_input, q_scale, q_min = ext_quantization.compress_single_precision(
-                _to_groups(input), q_bits, config.stochastic, stat_dtype=stat_dtype)
+                to_groups(input), q_bits, config.stochastic, stat_dtype=stat_dtype)
         else:
             groups, _, mn, mx = no_scheme_compute_quantization_bits(input)
             q_input, q_scale, q_min = ext_quantization.pack_single_precision(

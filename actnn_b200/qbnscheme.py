@@ -2,7 +2,8 @@
 preceding conv / linear layer (mirror of actnn/actnn/qbnscheme.py:9-60)."""
 from .conf import config
 from .cpp_extension import calc_precision as ext_calc_precision
-from .qscheme import QScheme, group_minimax, total_bits_after_greedy
+from .cpp_extension import quantization as ext_quantization
+from .qscheme import QScheme, group_minimax, to_groups, total_bits_after_greedy
 
 
 class QBNScheme(QScheme):
@@ -27,6 +28,18 @@ class QBNScheme(QScheme):
         b.word_offsets = offsets
         b.total_bits = total_bits_after_greedy(N, self.initial_bits, target)
         return groups, b, mn, mx
+
+    def compress(self, input, stat_dtype):
+        """One-call variant of ``compute_quantization_bits`` + pack (see ``QScheme.compress``)."""
+        if not config.pergroup:
+            return None
+        self.prev_linear = QScheme.prev_layer
+        N, D = input.shape[0], input.shape[1]
+        num_pixels = (input.numel() // N) // D
+        q_input, b, q_scale, q_min, _ = ext_quantization.compress_mixed_precision(
+            to_groups(input), int(self.bits * N), int(self.initial_bits), config.group_size / num_pixels,
+            1.0, None, config.stochastic, stat_dtype=stat_dtype)
+        return q_input, b, q_scale, q_min
 
     @staticmethod
     def allocate_perlayer():

@@ -12,11 +12,11 @@ import torch
 from .conf import config
 from .cpp_extension import calc_precision as ext_calc_precision
 from .cpp_extension import minimax as ext_minimax
+from .cpp_extension import quantization as ext_quantization
 
 
-def group_minimax(input: torch.Tensor):
-    """Flatten to ``[N, G, group_size]`` (zero-padding the tail of every sample, as
-    qscheme.py:61-71 does) and return ``(groups, mn[N,G,1], mx[N,G,1])``."""
+def to_groups(input: torch.Tensor) -> torch.Tensor:
+    """Flatten to ``[N, G, group_size]``, zero-padding the tail of every sample (qscheme.py:61-71)."""
     N = input.shape[0]
     gs = config.group_size
     flat = input.view(N, -1)
@@ -24,7 +24,14 @@ def group_minimax(input: torch.Tensor):
     if num_features % gs != 0:
         pad = (num_features // gs + 1) * gs - num_features
         flat = torch.cat([flat, torch.zeros([N, pad], dtype=input.dtype, device=input.device)], 1)
-    groups = flat.view(-1, gs)
+    return flat.view(N, -1, gs)
+
+
+def group_minimax(input: torch.Tensor):
+    """``(groups [N,G,gs], mn[N,G,1], mx[N,G,1])`` of an activation."""
+    N = input.shape[0]
+    gs = config.group_size
+    groups = to_groups(input).view(-1, gs)
     mn, mx = ext_minimax.minimax(groups)
     if not config.pergroup:                       # one range for the whole tensor
         mn = torch.ones_like(mn) * mn.min()
@@ -113,6 +120,28 @@ class QScheme(object):
         self.dim = input.numel() // N
         self.b = b
         return groups, b, mn, mx
+
+    def compress(self, input, stat_dtype):
+        """``compute_quantization_bits`` + mixed-precision pack as ONE native call (four kernel
+        launches, no host synchronisation).  Returns ``(q_input, q_bits, q_scale, q_min)``, or
+        ``None`` when a configuration needs the step-by-step path."""
+        grad = self.get_scale()
+        if not config.pergroup or grad.numel() != 1:
+            return None
+        QScheme.prev_layer = self
+        N, D = input.shape[0], input.shape[1]
+        num_pixels = (input.numel() // N) // D
+        if not grad.is_cuda or grad.dtype != torch.float32:
+            grad = grad.to(device=input.device, dtype=torch.float32)
+            self.scales = grad
+        q_input, b, q_scale, q_min, C = ext_quantization.compress_mixed_precision(
+            to_groups(input), int(self.bits * N), int(self.initial_bits), config.group_size / num_pixels,
+            self.num_locations / 4 / self.depthwise_groups, grad.reshape(1), config.stochastic,
+            stat_dtype=stat_dtype)
+        self.C = C
+        self.dim = input.numel() // N
+        self.b = b
+        return q_input, b, q_scale, q_min
 
     # ------------------------------------------------------------- per-layer bits
     @staticmethod

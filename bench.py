@@ -141,7 +141,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample_n = 16
+    sample_n = 64
     warm = max(args.warmup, 1)
     import torch  # noqa: F401
     gbs, sec, cores = cpu_round_trip_gbs(sample_n, args.steps, warmup=min(warm, 3))
@@ -200,14 +200,18 @@ def run_ours(args):
     mins = [torch.empty(N, G, 1, dtype=dt, device=dev) for _ in range(POOL)]
     outs = [torch.empty(N, G, gs, dtype=dt, device=dev) for _ in range(2)]
 
+    def cur_stream():
+        return torch.cuda.current_stream().cuda_stream
+
     def compress(i, step_no):
         _lib.check(lib.actnn_compress_single(xs[i].data_ptr(), bits, packed[i].data_ptr(), scales[i].data_ptr(),
                                              mins[i].data_ptr(), None, N, G, gs, F16, F16, 1, None, 1234 + rank,
-                                             4 * step_no, stream), "actnn_compress_single")
+                                             4 * step_no, cur_stream()), "actnn_compress_single")
 
     def decompress(i, o):
         _lib.check(lib.actnn_unpack_single(packed[i].data_ptr(), bits, scales[i].data_ptr(), mins[i].data_ptr(),
-                                           outs[o].data_ptr(), N, G, gs, F16, F16, stream), "actnn_unpack_single")
+                                           outs[o].data_ptr(), N, G, gs, F16, F16, cur_stream()),
+                   "actnn_unpack_single")
 
     def step(k):
         compress(k % POOL, k)
@@ -234,19 +238,35 @@ def run_ours(args):
                 k += 1
             torch.cuda.synchronize()
 
-        # ---- timed region: exactly K steps, CUDA events on the launching stream
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
-        barrier()
-        ev[0].record()
-        for k in range(args.steps):
-            compress(k % POOL, k)
-            ev[2 * k + 1].record()
-            decompress((k + POOL // 2) % POOL, k % 2)
-            ev[2 * k + 2].record()
-        barrier()
-    total_ms = ev[0].elapsed_time(ev[-1])
-    pack_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps)) / args.steps
-    unpack_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(args.steps)) / args.steps
+        # ---- timed region: exactly K steps.  The K steps are captured once into a CUDA graph
+        # (launch gaps of a few microseconds would otherwise be a tenth of a 25-microsecond
+        # kernel) and the replay is bracketed by CUDA events on the launching stream.
+        def graph_of(fn, count):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for k in range(count):
+                    fn(k)
+            return g
+
+        def timed_replay(g):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            a.record()
+            g.replay()
+            b.record()
+            barrier()
+            return a.elapsed_time(b)
+
+        g_steps = graph_of(step, args.steps)
+        g_steps.replay()
+        total_ms = timed_replay(g_steps)
+        # the two kernels of the step, each alone, same rotation (for the roofline figure)
+        g_pack = graph_of(lambda k: compress(k % POOL, k), args.steps)
+        g_unpack = graph_of(lambda k: decompress((k + POOL // 2) % POOL, k % 2), args.steps)
+        g_pack.replay()
+        pack_ms = timed_replay(g_pack) / args.steps
+        g_unpack.replay()
+        unpack_ms = timed_replay(g_unpack) / args.steps
     if world > 1:
         t = torch.tensor([total_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -361,7 +381,7 @@ def run_ours(args):
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": elements * 2,
                     "d2h_bytes_per_step": elements * 2, "ms_per_step": round(e2e_ms, 4),
                     "path": "pinned host -> H2D -> ops.quantize_activation -> ops.dequantize_activation -> D2H"},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": 2 * args.steps, "launch_mode": "the K steps replayed from one CUDA graph",
             "roofline": {"kernel": "pack_single_kernel<half, 2 bit, fused> (actnn_compress_single)", "bound": "hbm",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": peak_src,
@@ -370,11 +390,114 @@ def run_ours(args):
             "clocks": sampler.summary(),
         }
         if world == 1:
-            gbs, sec, cores = cpu_round_trip_gbs(16, repeats=5)
+            gbs, sec, cores = cpu_round_trip_gbs(256, repeats=30)
             line["cpu_baseline"] = {"value": round(gbs, 4), "unit": "GB/s", "cores": cores, "kind": "port",
-                                    "sample": "16 of the 256 samples, 5 passes (%.2f s each), CPU oracle = the "
-                                              "reference's simulate path restated for CPU tensors" % sec}
+                                    "sample": "the whole [256,256,28,28] activation, 30 passes (%.2f s each), CPU "
+                                              "oracle = the reference's simulate path restated for CPU tensors, "
+                                              "torch threads = cores" % sec}
         print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------
+# the callers of the path: ResNet-50 training step with compressed activations
+# ---------------------------------------------------------------------------------------
+def resnet_throughput(level: str, batch: int, steps: int, warmup: int, dev, world: int, arch: str = "resnet50",
+                      amp_dtype="float16"):
+    """images/s per GPU (median step, CUDA events) and activation bytes of one training step of a
+    torchvision ResNet (random init, synthetic 224x224 images) under ``actnn`` level `level`.
+    Protocols follow the reference's mem_speed_benchmark/train.py:363-438."""
+    import torch
+    import torch.nn as nn
+    import torchvision
+
+    import actnn_b200 as actnn
+    from actnn_b200.conf import QuantizationConfig
+
+    actnn.config.__dict__.update(QuantizationConfig().__dict__)
+    actnn.QScheme.layers.clear()
+    actnn.QBNScheme.layers.clear()
+    actnn.QScheme.num_layers = 0
+    actnn.set_optimization_level(level)
+    torch.manual_seed(0)
+    model = getattr(torchvision.models, arch)()
+    if world > 1:
+        model = nn.SyncBatchNorm.convert_sync_batchnorm(model)
+    if level != "exact":
+        model = actnn.QModule(model)
+    model = model.to(dev).train()
+    if world > 1:
+        model = nn.parallel.DistributedDataParallel(model, device_ids=[dev.index])
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
+    dt = getattr(torch, amp_dtype)
+    scaler = torch.amp.GradScaler("cuda", enabled=dt == torch.float16)
+    crit = nn.CrossEntropyLoss()
+    g = torch.Generator(device=dev).manual_seed(dev.index or 0)
+    images = torch.randn(batch, 3, 224, 224, device=dev, generator=g)
+    target = torch.randint(0, 1000, (batch,), device=dev, generator=g)
+    times, act_bytes = [], None
+    for it in range(warmup + steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        before = torch.cuda.memory_allocated(dev)
+        with torch.autocast("cuda", dtype=dt):
+            out = model(images)
+            loss = crit(out, target)
+        if it == warmup - 1:
+            act_bytes = torch.cuda.memory_allocated(dev) - before - out.numel() * out.element_size() - 4
+        opt.zero_grad(set_to_none=True)
+        scaler.scale(loss).backward()
+        scaler.step(opt)
+        scaler.update()
+        b.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            times.append(a.elapsed_time(b))
+    times.sort()
+    med = times[len(times) // 2]
+    peak = torch.cuda.max_memory_allocated(dev)
+    del model, opt, images, out, loss
+    torch.cuda.empty_cache()
+    return {"images_per_s_per_gpu": round(batch / med * 1e3, 1), "ms_per_step": round(med, 2),
+            "activation_bytes": int(act_bytes), "peak_bytes": int(peak)}
+
+
+def run_resnet(args):
+    """`--workload resnet50`: whole-job images/s of L3 training next to exact training."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    steps, warm = max(3, min(args.steps, 30)), max(3, min(args.warmup, 5))
+    res = {}
+    for level in ("exact", args.level):
+        res[level] = resnet_throughput(level, args.batch, steps, warm, dev, world, args.arch, args.amp)
+        if world > 1:
+            t = torch.tensor([res[level]["ms_per_step"]], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[level]["ms_per_step"] = float(t.item())
+            res[level]["images_per_s_per_gpu"] = round(args.batch / float(t.item()) * 1e3, 1)
+    if rank == 0:
+        q, e = res[args.level], res["exact"]
+        print(json.dumps({
+            "metric": "%s %s images/s" % (args.arch, args.level), "value": round(q["images_per_s_per_gpu"] * world, 1),
+            "unit": "images/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": q["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.amp, "data": "synthetic",
+            "config": {"workload": "%s-%s-training" % (args.arch, args.level), "batch_per_gpu": args.batch,
+                       "image": [3, 224, 224], "optimizer": "SGD momentum 0.9", "parallelism": "ddp x%d" % world,
+                       "sync_bn": world > 1},
+            "exact_images_per_s": round(e["images_per_s_per_gpu"] * world, 1),
+            "ratio_to_exact": round(q["images_per_s_per_gpu"] / e["images_per_s_per_gpu"], 4),
+            "activation_bytes": q["activation_bytes"], "exact_activation_bytes": e["activation_bytes"],
+            "activation_reduction_vs_%s_autocast" % args.amp: round(e["activation_bytes"] / max(q["activation_bytes"], 1), 2),
+        }))
     if world > 1:
         dist.destroy_process_group()
 
@@ -447,6 +570,12 @@ def run_profile(args):
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="codec", choices=["codec", "resnet"],
+                    help="codec (default, the headline metric) or a ResNet training step through the Q-layers")
+    ap.add_argument("--arch", default="resnet50")
+    ap.add_argument("--level", default="L3")
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--amp", default="float16", choices=["float16", "bfloat16"])
     ap.add_argument("--profile", default=None, help="run a few launches of one kernel (for ncu); 'all' = each")
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--gpus", type=int, default=1)
@@ -456,6 +585,8 @@ def main():
     args = ap.parse_args()
     if args.profile:
         run_profile(args)
+    elif args.workload == "resnet":
+        run_resnet(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -26,7 +26,7 @@
  *     values in [-0.5, 0.5]) to inject it, or NULL to draw it in registers from
  *     Philox4x32-10 keyed by (seed, offset); actnn_noise_fill() materialises exactly that
  *     stream.  `stochastic == 0` rounds to nearest without noise.
- *   - a NaN input is encoded as code 0.
+ *   - a NaN input yields some valid code (0 or the largest); it never corrupts its neighbours.
  */
 #ifndef ACTNN_B200_H_
 #define ACTNN_B200_H_
@@ -159,6 +159,27 @@ int actnn_range_sqr(const void* mn, const void* mx, int64_t N, int64_t G, int st
 int actnn_calc_precision(const float* C, const int32_t* w, int64_t N, int initial_bits,
                          double target, int32_t* b_out, int64_t* word_offsets,
                          int64_t G, int64_t group_size, actnn_stream_t stream);
+
+/* The adaptive compress of one activation as one call: per-group min/max, sensitivities,
+ * greedy allocation at `target` total bits, scale + stochastic rounding + mixed-precision
+ * pack.  Replaces the sequence QScheme.compute_quantization_bits -> quantize_and_pack,
+ * actnn/actnn/qscheme.py:57-94 and actnn/actnn/ops.py:44-48 (there: ~15 launches, two host
+ * copies and a CPU heap).  Outputs: packed (the caller sizes it for the bit total the greedy
+ * will reach: min(initial_bits*N, max(target, N)) * G * group_size / 32 words), scale and
+ * mn_out [N,G] (`stat_dtype`), bits_out [N], word_offsets_out [N+1], C_out [N] (float32
+ * sensitivities, kept by the caller for the per-layer allocation).
+ * `workspace` is caller-provided scratch of at least actnn_compress_mixed_workspace(N, G,
+ * dtype) bytes, 256-byte aligned; it holds the per-group min / max between the kernels and
+ * its content afterwards is unspecified.  Arguments otherwise as in actnn_range_sqr,
+ * actnn_calc_precision and actnn_pack_mixed. */
+int64_t actnn_compress_mixed_workspace(int64_t N, int64_t G, int dtype);
+int actnn_compress_mixed(const void* data, int32_t* packed, void* scale, void* mn_out,
+                         int32_t* bits_out, int64_t* word_offsets_out, float* C_out,
+                         void* workspace, int64_t workspace_bytes, int64_t N, int64_t G,
+                         int64_t group_size, int dtype, int stat_dtype, float range_factor,
+                         float coeff, const float* grad_scale, int initial_bits, double target,
+                         int stochastic, const void* noise, uint64_t seed, uint64_t offset,
+                         actnn_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * Mask ops.  The saved mask is 1 bit per element: bit (e % 8) of byte e / 8, padded to

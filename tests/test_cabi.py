@@ -29,7 +29,7 @@ def test_header_and_binding_agree(lib):
     assert len(names) >= 18
     for name in names:
         assert hasattr(lib, name), "libactnn_b200.so does not export " + name
-    bound = set(_lib.SIGNATURES) | {"actnn_status_string", "actnn_abi_version"}
+    bound = set(_lib.SIGNATURES) | {"actnn_status_string", "actnn_abi_version", "actnn_compress_mixed_workspace"}
     assert bound == set(names)
 
 
@@ -40,7 +40,7 @@ def test_every_entry_point_cites_the_reference():
     for name in declared_functions():
         if name in ("actnn_status_string", "actnn_abi_version"):
             continue
-        head = text[:text.index("int " + name + "(")]
+        head = text[:re.search(r"\b(int|int64_t) " + name + r"\(", text).start()]
         section = head[head.rindex("/* ------"):]
         assert re.search(r"\.(cc|cu|py):\d+", section) or "counterpart" in section, name
 
@@ -82,6 +82,15 @@ def test_host_side_validation_needs_no_gpu(lib):
     assert lib.actnn_max_pool2d_forward(None, None, None, 1, 1, 8, 8, 4, 4, 1, 1, 0, 0, 1, 1, 0, None) == ARG
     assert lib.actnn_max_pool2d_forward(None, None, None, 1, 1, 8, 8, 2, 2, 2, 2, 0, 0, 1, 1, 0, None) == NULL
     assert lib.actnn_noise_fill(None, 8, 0, 1, 2, None) == NULL
+    # one-call adaptive compress: workspace size and capacity check
+    assert lib.actnn_compress_mixed_workspace(4, 3, 1) == 2 * 256
+    assert lib.actnn_compress_mixed_workspace(512, 784, 0) == 2 * 512 * 784 * 4
+    assert lib.actnn_compress_mixed_workspace(-1, 3, 1) == -1
+    args = [256] * 8 + [8, 4, 3, 256, 1, 1, 1.0, 1.0, None, 8, 8.0, 1, None, 0, 0, None]
+    assert lib.actnn_compress_mixed(*args) == 8                      # ACTNN_ERR_CAPACITY: workspace too small
+    args[8] = 1 << 20
+    args[11] = 128
+    assert lib.actnn_compress_mixed(*args) == SHAPE
 
 
 def test_missing_library_is_an_error(monkeypatch, tmp_path):

@@ -342,3 +342,39 @@ def test_pack_argument_errors(ext):
     with pytest.raises(RuntimeError):                                  # misaligned view -> status from the C ABI
         flat = torch.zeros(2 * 2 * 256 + 8, device="cuda", dtype=torch.float16)
         ext.q.compress_single_precision(flat[1:1 + 1024].view(2, 2, 256), 2)
+
+
+# ------------------------------------------------------------------------------ one-call adaptive compress
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("shape", [(12, 16, 16, 16), (5, 8, 16, 16), (16, 2048)])
+def test_compress_mixed_one_call_equals_stepwise_and_oracle(ext, dtype, shape):
+    x = make_input(shape, dtype, sum(shape), "scaled")
+    n = shape[0]
+    groups = O.to_groups(x)
+    g = groups.shape[1]
+    num_pixels = groups.numel() // n // shape[1]
+    stat = torch.bfloat16 if dtype == torch.float32 else dtype
+    grad = torch.tensor([0.37], device="cuda")
+    seed, offset = 77, 16
+    packed, bits, scale, mn, C = ext.q.compress_mixed_precision(
+        dev(groups), 2 * n, 8, 256 / num_pixels, 9 / 4, grad, True, philox=(seed, offset), stat_dtype=stat)
+    # stepwise path through the individual entry points
+    dmn, dmx = ext.mm.minimax(dev(groups).view(-1, 256))
+    C2 = ext.cp.sensitivity(dmn.view(n, g, 1), dmx.view(n, g, 1), n, 256 / num_pixels, 9 / 4, grad)
+    bits2, offs2 = ext.cp.allocate_bits(C2, 8, 2 * n, None, g, 256, with_offsets=True)
+    p2, s2, m2 = ext.q.pack_mixed_precision(dev(groups), dmn.view(n, g, 1), dmx.view(n, g, 1), bits2, True,
+                                            philox=(seed, offset), word_offsets=offs2, total_bits=2 * n,
+                                            stat_dtype=stat, return_min=True)
+    assert torch.equal(C, C2) and torch.equal(bits, bits2) and torch.equal(packed.word_offsets, offs2)
+    assert torch.equal(packed, p2) and torch.equal(scale, s2) and torch.equal(mn, m2)
+    assert int(bits.sum()) == 2 * n and packed.numel() == 2 * n * g * 256 // 32
+    # and against the oracle, replaying the Philox noise
+    omn, omx = O.group_minimax(groups)
+    obits = O.calc_precision(torch.ones(n, dtype=torch.int32) * 8, C.cpu(), torch.ones(n, dtype=torch.int32), 2 * n)
+    assert torch.equal(bits.cpu(), obits)
+    noise = O.philox_noise(groups.numel(), dtype, seed, offset).view(groups.shape)
+    codes, oscale = O.quantize(groups, obits, omn, omx, noise)
+    assert np.array_equal(packed.cpu().numpy(), O.pack_mixed_layout(codes, obits))
+    assert same_values(scale.cpu(), oscale.to(stat)) and same_values(mn.cpu(), omn.to(stat))
+    out = ext.q.unpack_mixed_precision(packed, bits, scale, mn, n, g, 256, out_dtype=dtype)
+    assert same_values(out.cpu(), O.dequantize(codes, oscale.to(stat).to(dtype), omn.to(stat).to(dtype)))
