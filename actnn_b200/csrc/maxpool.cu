@@ -18,61 +18,100 @@ struct PoolGeom {
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-max_pool_forward_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t* __restrict__ idx, int64_t total,
+max_pool_forward_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t* __restrict__ idx, int planes,
                         PoolGeom g) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t id = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; id < total; id += stride) {
-    const int wo = (int)(id % g.Wo);
-    const int64_t t = id / g.Wo;
-    const int ho = (int)(t % g.Ho);
-    const int64_t nc = t / g.Ho;
-    const T* plane = x + nc * ((int64_t)g.H * g.W);
-    const int hb = ho * g.SH - g.PH, wb = wo * g.SW - g.PW;
-    float best = -INFINITY;
-    int arg = 0;
-    for (int kh = 0; kh < g.KH; ++kh) {
-      const int h = hb + kh * g.DH;
-      if (h < 0 || h >= g.H) continue;
-      for (int kw = 0; kw < g.KW; ++kw) {
-        const int w = wb + kw * g.DW;
-        if (w < 0 || w >= g.W) continue;
-        const float v = load_scalar<T>(plane, (int64_t)h * g.W + w);
-        if (v > best) { best = v; arg = kh * g.KW + kw; }
+  // blockIdx.y strides over the (n, c) planes; 32-bit index arithmetic inside a plane
+  const int plane_elems = g.H * g.W, out_elems = g.Ho * g.Wo;
+  for (int nc = blockIdx.y; nc < planes; nc += gridDim.y) {
+    const T* plane = x + (int64_t)nc * plane_elems;
+    T* y_p = y + (int64_t)nc * out_elems;
+    int8_t* idx_p = idx + (int64_t)nc * out_elems;
+    for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < out_elems; o += gridDim.x * blockDim.x) {
+      const int ho = o / g.Wo, wo = o - ho * g.Wo;
+      const int hb = ho * g.SH - g.PH, wb = wo * g.SW - g.PW;
+      float best = -INFINITY;
+      int arg = 0;
+      for (int kh = 0; kh < g.KH; ++kh) {
+        const int h = hb + kh * g.DH;
+        if (h < 0 || h >= g.H) continue;
+        for (int kw = 0; kw < g.KW; ++kw) {
+          const int w = wb + kw * g.DW;
+          if (w < 0 || w >= g.W) continue;
+          const float v = load_scalar<T>(plane, h * g.W + w);
+          if (v > best) { best = v; arg = kh * g.KW + kw; }
+        }
       }
+      store_scalar<T>(y_p, o, best);
+      idx_p[o] = (int8_t)arg;
     }
-    store_scalar<T>(y, id, best);
-    idx[id] = (int8_t)arg;
   }
 }
 
 template <typename T>
+int launch_forward(const void* x, void* y, int8_t* idx, int64_t planes, const PoolGeom& g, cudaStream_t s) {
+  const int out_elems = g.Ho * g.Wo;
+  dim3 grid((unsigned)min(64, (out_elems + 255) / 256), (unsigned)min((int64_t)65535, planes));
+  max_pool_forward_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (T*)y, idx, (int)planes, g);
+  return check_launch();
+}
+
+// Backward.  One block row per (n, c) plane (blockIdx.y strides over planes), threads over
+// the plane's positions, all index arithmetic in 32 bits.  STRIDE / UNIT_DILATION are
+// compile-time for the common geometries (stride 1 or 2, dilation 1) so that the divisions
+// become shifts; STRIDE == 0 is the general case.  Only the output rows / columns whose
+// window can contain the position are visited:
+//   ho in [ceil((h + PH - (KH-1)*DH) / SH), floor((h + PH) / SH)].
+template <typename T, int STRIDE, bool UNIT_DILATION>
 __global__ void __launch_bounds__(256)
 max_pool_backward_kernel(const T* __restrict__ gy, const int8_t* __restrict__ idx, T* __restrict__ gx,
-                         int64_t total, PoolGeom g) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t id = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; id < total; id += stride) {
-    const int w = (int)(id % g.W);
-    const int64_t t = id / g.W;
-    const int h = (int)(t % g.H);
-    const int64_t nc = t / g.H;
-    const int64_t obase = nc * ((int64_t)g.Ho * g.Wo);
-    float acc = 0.f;
-    for (int kh = 0; kh < g.KH; ++kh) {
-      const int hh = h + g.PH - kh * g.DH;
-      if (hh < 0 || hh % g.SH != 0) continue;
-      const int ho = hh / g.SH;
-      if (ho >= g.Ho) continue;
-      for (int kw = 0; kw < g.KW; ++kw) {
-        const int ww = w + g.PW - kw * g.DW;
-        if (ww < 0 || ww % g.SW != 0) continue;
-        const int wo = ww / g.SW;
-        if (wo >= g.Wo) continue;
-        const int64_t o = obase + (int64_t)ho * g.Wo + wo;
-        if (idx[o] == (int8_t)(kh * g.KW + kw)) acc += load_scalar<T>(gy, o);
+                         int planes, PoolGeom g) {
+  const int SH = STRIDE ? STRIDE : g.SH, SW = STRIDE ? STRIDE : g.SW;
+  const int DH = UNIT_DILATION ? 1 : g.DH, DW = UNIT_DILATION ? 1 : g.DW;
+  const int plane_elems = g.H * g.W, out_elems = g.Ho * g.Wo;
+  const int reach_h = (g.KH - 1) * DH, reach_w = (g.KW - 1) * DW;
+  for (int nc = blockIdx.y; nc < planes; nc += gridDim.y) {
+    const T* gy_p = gy + (int64_t)nc * out_elems;
+    const int8_t* idx_p = idx + (int64_t)nc * out_elems;
+    T* gx_p = gx + (int64_t)nc * plane_elems;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < plane_elems; e += gridDim.x * blockDim.x) {
+      const int h = e / g.W, w = e - h * g.W;
+      const int ah = h + g.PH, aw = w + g.PW;                    // >= 0
+      const int ho_hi = min(g.Ho - 1, ah / SH), wo_hi = min(g.Wo - 1, aw / SW);
+      const int ho_lo = ah > reach_h ? (ah - reach_h + SH - 1) / SH : 0;
+      const int wo_lo = aw > reach_w ? (aw - reach_w + SW - 1) / SW : 0;
+      float acc = 0.f;
+      for (int ho = ho_lo; ho <= ho_hi; ++ho) {
+        const int dh = ah - ho * SH;                              // = kh * DH if this row has a tap on h
+        const int kh = UNIT_DILATION ? dh : dh / DH;
+        if (!UNIT_DILATION && kh * DH != dh) continue;
+        for (int wo = wo_lo; wo <= wo_hi; ++wo) {
+          const int dw = aw - wo * SW;
+          const int kw = UNIT_DILATION ? dw : dw / DW;
+          if (!UNIT_DILATION && kw * DW != dw) continue;
+          const int o = ho * g.Wo + wo;
+          if (idx_p[o] == (int8_t)(kh * g.KW + kw)) acc += load_scalar<T>(gy_p, o);
+        }
       }
+      store_scalar<T>(gx_p, e, acc);
     }
-    store_scalar<T>(gx, id, acc);
   }
+}
+
+template <typename T>
+int launch_backward(const void* gy, const int8_t* idx, void* gx, int64_t planes, const PoolGeom& g, cudaStream_t s) {
+  const int plane_elems = g.H * g.W;
+  dim3 grid((unsigned)min(64, (plane_elems + 255) / 256), (unsigned)min((int64_t)65535, planes));
+  const bool unit = g.DH == 1 && g.DW == 1;
+  const int p = (int)planes;
+  if (unit && g.SH == 2 && g.SW == 2)
+    max_pool_backward_kernel<T, 2, true><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, p, g);
+  else if (unit && g.SH == 1 && g.SW == 1)
+    max_pool_backward_kernel<T, 1, true><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, p, g);
+  else if (unit)
+    max_pool_backward_kernel<T, 0, true><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, p, g);
+  else
+    max_pool_backward_kernel<T, 0, false><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, p, g);
+  return check_launch();
 }
 
 int check_geom(int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW, int SH, int SW, int PH, int PW, int DH,
@@ -85,10 +124,6 @@ int check_geom(int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW, int S
   if (Ho <= 0 || Wo <= 0) return ACTNN_ERR_SHAPE;
   *g = PoolGeom{(int)H, (int)W, (int)Ho, (int)Wo, KH, KW, SH, SW, PH, PW, DH, DW};
   return ACTNN_OK;
-}
-
-int grid_for(int64_t total) {
-  return (int)max((int64_t)1, min((total + 255) / 256, (int64_t)device_info().sm_count * 16));
 }
 
 }  // namespace
@@ -104,21 +139,14 @@ extern "C" int actnn_max_pool2d_forward(const void* x, void* y, int8_t* idx, int
   const int64_t total = N * C * g.Ho * g.Wo;
   if (total == 0) return ACTNN_OK;
   if (!x || !y || !idx) return ACTNN_ERR_NULL;
+  if (N * C > 0x7fffffff || H * W > 0x7fffffff) return ACTNN_ERR_SHAPE;
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
-    case ACTNN_F32:
-      max_pool_forward_kernel<float><<<grid_for(total), 256, 0, s>>>((const float*)x, (float*)y, idx, total, g);
-      break;
-    case ACTNN_F16:
-      max_pool_forward_kernel<__half><<<grid_for(total), 256, 0, s>>>((const __half*)x, (__half*)y, idx, total, g);
-      break;
-    case ACTNN_BF16:
-      max_pool_forward_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, s>>>((const __nv_bfloat16*)x,
-                                                                            (__nv_bfloat16*)y, idx, total, g);
-      break;
+    case ACTNN_F32: return launch_forward<float>(x, y, idx, N * C, g, s);
+    case ACTNN_F16: return launch_forward<__half>(x, y, idx, N * C, g, s);
+    case ACTNN_BF16: return launch_forward<__nv_bfloat16>(x, y, idx, N * C, g, s);
     default: return ACTNN_ERR_DTYPE;
   }
-  return check_launch();
 }
 
 extern "C" int actnn_max_pool2d_backward(const void* grad_out, const int8_t* idx, void* grad_in, int64_t N,
@@ -127,23 +155,15 @@ extern "C" int actnn_max_pool2d_backward(const void* grad_out, const int8_t* idx
   PoolGeom g;
   if (int st = check_geom(N, C, H, W, KH, KW, SH, SW, PH, PW, DH, DW, &g)) return st;
   const int64_t total = N * C * H * W;
+  const int64_t planes = N * C;
   if (total == 0) return ACTNN_OK;
   if (!grad_out || !idx || !grad_in) return ACTNN_ERR_NULL;
+  if (planes > 0x7fffffff || H * W > 0x7fffffff) return ACTNN_ERR_SHAPE;
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
-    case ACTNN_F32:
-      max_pool_backward_kernel<float><<<grid_for(total), 256, 0, s>>>((const float*)grad_out, idx, (float*)grad_in,
-                                                                      total, g);
-      break;
-    case ACTNN_F16:
-      max_pool_backward_kernel<__half><<<grid_for(total), 256, 0, s>>>((const __half*)grad_out, idx,
-                                                                       (__half*)grad_in, total, g);
-      break;
-    case ACTNN_BF16:
-      max_pool_backward_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, s>>>(
-          (const __nv_bfloat16*)grad_out, idx, (__nv_bfloat16*)grad_in, total, g);
-      break;
+    case ACTNN_F32: return launch_backward<float>(grad_out, idx, grad_in, planes, g, s);
+    case ACTNN_F16: return launch_backward<__half>(grad_out, idx, grad_in, planes, g, s);
+    case ACTNN_BF16: return launch_backward<__nv_bfloat16>(grad_out, idx, grad_in, planes, g, s);
     default: return ACTNN_ERR_DTYPE;
   }
-  return check_launch();
 }

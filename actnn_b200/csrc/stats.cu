@@ -257,6 +257,110 @@ greedy_kernel(const float* __restrict__ C, const int32_t* __restrict__ w, int64_
   if (word_offsets && tid == 0) word_offsets[N] = carry * words_per_bit;
 }
 
+// Fast path for unit weights and few candidates (the per-layer call of every training step):
+// every thread keeps its candidate keys in registers and the threshold is found four bits
+// per block-wide pass (15 trial thresholds at once) instead of one, skipping the bits of
+// the key that are zero for every candidate.  THREADS * kCache keys at most.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+greedy_small_kernel(const float* __restrict__ C, int64_t N, int initial_bits, double target, GreedyCoef coef,
+                    int32_t* __restrict__ b_out, int64_t* __restrict__ word_offsets, int64_t words_per_bit) {
+  constexpr int WARPS = THREADS / 32;
+  __shared__ uint32_t part[2][WARPS][8];                       // 15 counts, two per word
+  __shared__ int scan_sums[WARPS];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int per = initial_bits - 1;
+  const int64_t total = N * per;
+  const int64_t b_sum0 = N * initial_bits;
+  const double deficit = (double)b_sum0 - target;
+  const int64_t need = deficit > 0.0 ? (int64_t)ceil(deficit) : 0;
+
+  uint64_t keys[kCache];
+#pragma unroll
+  for (int k = 0; k < kCache; ++k) {
+    const int64_t cidx = (int64_t)tid + (int64_t)k * THREADS;
+    keys[k] = 0;                                               // below every real key (b >= 2)
+    if (cidx < total) {
+      const int64_t i = cidx / per;
+      keys[k] = candidate_key(C[i], 1, initial_bits - (int)(cidx - i * per), i, coef);
+    }
+  }
+  // bits of the low word that can be set: (i << 5) | b with i < N
+  int low_bits = 5;
+  while (((int64_t)1 << (low_bits - 5)) < N) ++low_bits;
+  low_bits = (low_bits + 3) & ~3;
+
+  uint64_t T = 0;
+  if (need == 0) {
+    T = ~0ull;
+  } else if (need >= total) {
+    T = 1;                                                     // every candidate is taken
+  } else {
+    int buf = 0;
+    for (int shift = 60; shift >= 0; shift -= 4) {
+      if (shift < 32 && shift >= low_bits) continue;           // always-zero key bits
+      uint32_t cnt[8];
+#pragma unroll
+      for (int w = 0; w < 8; ++w) cnt[w] = 0;
+#pragma unroll
+      for (int j = 1; j < 16; ++j) {
+        const uint64_t trial = T | ((uint64_t)j << shift);
+        uint32_t c = 0;
+#pragma unroll
+        for (int k = 0; k < kCache; ++k) c += keys[k] >= trial ? 1u : 0u;
+        cnt[j >> 1] += c << (16 * (j & 1));
+      }
+#pragma unroll
+      for (int w = 0; w < 8; ++w) cnt[w] = __reduce_add_sync(kFull, cnt[w]);
+      if (lane < 8) part[buf][wid][lane] = cnt[lane];
+      __syncthreads();
+      int digit = 0;
+#pragma unroll
+      for (int j = 1; j < 16; ++j) {
+        uint32_t tot = 0;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) tot += (part[buf][w][j >> 1] >> (16 * (j & 1))) & 0xffffu;
+        if ((int64_t)tot >= need) digit = j;                   // counts fall as j grows
+      }
+      T |= (uint64_t)digit << shift;
+      buf ^= 1;
+    }
+  }
+  // widths and word offsets (N <= THREADS * kCache / per, one or more rounds of THREADS)
+  int carry = 0;
+  for (int64_t start = 0; start < N; start += THREADS) {
+    const int64_t i = start + tid;
+    int b = 0;
+    if (i < N) {
+      const float c = C[i];
+      b = initial_bits;
+      for (int bb = initial_bits; bb >= 2; --bb) b -= candidate_key(c, 1, bb, i, coef) >= T ? 1 : 0;
+      b_out[i] = b;
+    }
+    if (word_offsets) {
+      int incl = b;
+#pragma unroll
+      for (int s = 1; s < 32; s <<= 1) {
+        const int t = __shfl_up_sync(kFull, incl, s);
+        if (lane >= s) incl += t;
+      }
+      __syncthreads();
+      if (lane == 31) scan_sums[wid] = incl;
+      __syncthreads();
+      int before = 0, block_total = 0;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const int v = scan_sums[w];
+        before += w < wid ? v : 0;
+        block_total += v;
+      }
+      if (i < N) word_offsets[i] = (int64_t)(carry + before + incl - b) * words_per_bit;
+      carry += block_total;
+    }
+  }
+  if (word_offsets && tid == 0) word_offsets[N] = (int64_t)carry * words_per_bit;
+}
+
 }  // namespace
 }  // namespace actnn
 
@@ -327,7 +431,12 @@ extern "C" int actnn_calc_precision(const float* C, const int32_t* w, int64_t N,
   }
   const int64_t wpb = word_offsets ? G * group_size / 32 : 0;
   cudaStream_t s = (cudaStream_t)stream;
+  const int64_t candidates = N * (initial_bits - 1);
   if (w) greedy_kernel<true><<<1, kGreedyThreads, 0, s>>>(C, w, N, initial_bits, target, coef, b_out, word_offsets, wpb);
+  else if (candidates <= 256 * kCache)
+    greedy_small_kernel<256><<<1, 256, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
+  else if (candidates <= 1024 * kCache)
+    greedy_small_kernel<1024><<<1, 1024, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
   else greedy_kernel<false><<<1, kGreedyThreads, 0, s>>>(C, w, N, initial_bits, target, coef, b_out, word_offsets, wpb);
   return check_launch();
 }

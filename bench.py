@@ -419,7 +419,8 @@ def resnet_throughput(level: str, batch: int, steps: int, warmup: int, dev, worl
     actnn.QScheme.layers.clear()
     actnn.QBNScheme.layers.clear()
     actnn.QScheme.num_layers = 0
-    actnn.set_optimization_level(level)
+    if level != "exact":
+        actnn.set_optimization_level(level)
     torch.manual_seed(0)
     model = getattr(torchvision.models, arch)()
     if world > 1:
