@@ -50,6 +50,26 @@ def algorithmic_bytes(elements: int, elem_size: int, bits: float, stat_size: int
 
 
 # ---------------------------------------------------------------------------------------
+# multi-rank bookkeeping (one process per GPU; the codec itself needs no collective)
+# ---------------------------------------------------------------------------------------
+def max_over_ranks(local_ms: float, device=None) -> float:
+    """The slowest rank's time: the whole job is as slow as its slowest replica."""
+    import torch
+    import torch.distributed as dist
+
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(local_ms)
+    t = torch.tensor([float(local_ms)], dtype=torch.float64, device=device or "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_gbs(bytes_per_rank_step: float, world: int, ms_per_step: float) -> float:
+    """Aggregate throughput of `world` replicas that each move `bytes_per_rank_step` per step."""
+    return world * bytes_per_rank_step / (ms_per_step * 1e-3) / 1e9
+
+
+# ---------------------------------------------------------------------------------------
 # clocks: sampled with NVML from a side thread while the GPU is under load
 # ---------------------------------------------------------------------------------------
 class ClockSampler:
@@ -267,12 +287,9 @@ def run_ours(args):
         pack_ms = timed_replay(g_pack) / args.steps
         g_unpack.replay()
         unpack_ms = timed_replay(g_unpack) / args.steps
-    if world > 1:
-        t = torch.tensor([total_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+    total_ms = max_over_ranks(total_ms, dev)
     ms_per_step = total_ms / args.steps
-    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    value = whole_job_gbs(step_bytes, world, ms_per_step)
 
     # ---- other kernels of the path, each timed alone over the rotating pool (informational)
     def time_kernel(fn, reps=16):
@@ -352,11 +369,8 @@ def run_ours(args):
     b.record()
     barrier()
     e2e_ms = a.elapsed_time(b) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
+    e2e_ms = max_over_ranks(e2e_ms, dev)
+    e2e_value = whole_job_gbs(step_bytes, world, e2e_ms)
 
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
