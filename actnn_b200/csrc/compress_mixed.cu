@@ -41,3 +41,56 @@ extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* sca
   return actnn_pack_mixed(data, mn, mx, bits_out, word_offsets_out, packed, scale, mn_out, N, G, group_size, dtype,
                           stat_dtype, stochastic, noise, seed, offset, stream);
 }
+
+// ------------------------------------------------------------------------------------------
+// The same compress for callers that have no way to provide scratch memory.
+//
+// Some users of this library only ever hold pointers that somebody else handed to them: a
+// plug-in inside a host framework that owns every byte of device memory and exposes no
+// allocator to it, or a job whose device memory was carved up in advance by a memory plan
+// so that any further cudaMalloc may fail or disturb the plan.  For them the per-group
+// min / max that live between the four kernels go to a fixed array inside the library
+// instead of a caller workspace.  The price: the array (kStaticScratchBytes) is resident on
+// every GPU that loads the library until the process exits, and the problem size is capped.
+namespace {
+
+constexpr int64_t kStaticScratchBytes = 4 << 20;          // 4 MiB: N * G <= 1 Mi groups of 16-bit data
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device, looked up once per device.  In
+// host code the array's name is only a handle, not an address a kernel could use.
+int static_scratch_address(void** out) {
+  static void* addr[64];
+  static bool ready[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ACTNN_ERR_ARG;
+  if (!ready[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return ACTNN_ERR_LAUNCH;
+    addr[dev] = p;
+    ready[dev] = true;
+  }
+  *out = addr[dev];
+  return ACTNN_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t actnn_compress_mixed_static_capacity(void) { return kStaticScratchBytes; }
+
+extern "C" int actnn_compress_mixed_static(const void* data, int32_t* packed, void* scale, void* mn_out,
+                                           int32_t* bits_out, int64_t* word_offsets_out, float* C_out, int64_t N,
+                                           int64_t G, int64_t group_size, int dtype, int stat_dtype,
+                                           float range_factor, float coeff, const float* grad_scale,
+                                           int initial_bits, double target, int stochastic, const void* noise,
+                                           uint64_t seed, uint64_t offset, actnn_stream_t stream) {
+  const int64_t need = actnn_compress_mixed_workspace(N, G, dtype);
+  if (need < 0) return (N < 0 || G < 0) ? ACTNN_ERR_SHAPE : ACTNN_ERR_DTYPE;
+  if (need > kStaticScratchBytes) return ACTNN_ERR_CAPACITY;
+  void* scratch = nullptr;
+  if (int st = static_scratch_address(&scratch)) return st;
+  return actnn_compress_mixed(data, packed, scale, mn_out, bits_out, word_offsets_out, C_out, scratch,
+                              kStaticScratchBytes, N, G, group_size, dtype, stat_dtype, range_factor, coeff,
+                              grad_scale, initial_bits, target, stochastic, noise, seed, offset, stream);
+}

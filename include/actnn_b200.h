@@ -181,6 +181,32 @@ int actnn_compress_mixed(const void* data, int32_t* packed, void* scale, void* m
                          int stochastic, const void* noise, uint64_t seed, uint64_t offset,
                          actnn_stream_t stream);
 
+/* actnn_compress_mixed for callers that cannot hand over scratch memory.  (This entry point
+ * has no counterpart in the reference.)
+ * Who needs it: code that only works with pointers it was given -- a plug-in of a host
+ * framework that owns all device memory and offers no allocator, or a job whose device
+ * memory was planned out in advance so that one more cudaMalloc may fail or upset the plan.
+ * Same arguments and results as actnn_compress_mixed without `workspace`: the per-group
+ * min / max go to an array of actnn_compress_mixed_static_capacity() bytes (4 MiB) that is
+ * part of the library image, i.e. resident on every GPU that loads the library until the
+ * process ends.  Limits and rules:
+ *   - actnn_compress_mixed_workspace(N, G, dtype) must not exceed the capacity (N*G up to
+ *     1 Mi groups of 16-bit data, 512 Ki of float32); larger problems return
+ *     ACTNN_ERR_CAPACITY and nothing is launched;
+ *   - the first call on a device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture begins;
+ *   - every call on a device uses the same array and leaves its last contents behind (no
+ *     part of it needs clearing: each call overwrites what it reads); two calls that may
+ *     overlap on the GPU (different streams) race on it -- serialise them;
+ *   - it never calls cudaMalloc, cudaFree or any allocating routine. */
+int64_t actnn_compress_mixed_static_capacity(void);
+int actnn_compress_mixed_static(const void* data, int32_t* packed, void* scale, void* mn_out,
+                                int32_t* bits_out, int64_t* word_offsets_out, float* C_out,
+                                int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype,
+                                float range_factor, float coeff, const float* grad_scale,
+                                int initial_bits, double target, int stochastic, const void* noise,
+                                uint64_t seed, uint64_t offset, actnn_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * Mask ops.  The saved mask is 1 bit per element: bit (e % 8) of byte e / 8, padded to
  * whole int32 words (mask_words = ceil(numel / 32)).

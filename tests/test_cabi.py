@@ -29,7 +29,8 @@ def test_header_and_binding_agree(lib):
     assert len(names) >= 18
     for name in names:
         assert hasattr(lib, name), "libactnn_b200.so does not export " + name
-    bound = set(_lib.SIGNATURES) | {"actnn_status_string", "actnn_abi_version", "actnn_compress_mixed_workspace"}
+    bound = set(_lib.SIGNATURES) | {"actnn_status_string", "actnn_abi_version", "actnn_compress_mixed_workspace",
+                                     "actnn_compress_mixed_static_capacity"}
     assert bound == set(names)
 
 
