@@ -34,7 +34,8 @@ SIGNATURES = {
     "actnn_compress_mixed_static": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _F, _F, _P, _I, _D, _I, _P, _U,
                                     _U, _P],
     "actnn_range_sqr": [_P, _P, _L, _L, _I, _F, _F, _P, _P, _P],
-    "actnn_calc_precision": [_P, _P, _L, _I, _D, _P, _P, _L, _L, _P],
+    "actnn_sample_sumsq": [_P, _P, _L, _L, _I, _P],
+    "actnn_calc_precision": [_P, _P, _L, _I, _D, _P, _P, _L, _L, _P, _L, _P],
     "actnn_relu_forward": [_P, _P, _P, _L, _I, _P],
     "actnn_relu_backward": [_P, _P, _P, _L, _I, _P],
     "actnn_dropout_forward": [_P, _P, _P, _L, _F, _I, _P, _U, _U, _P],
@@ -67,6 +68,8 @@ def load() -> ctypes.CDLL:
         lib.actnn_abi_version.restype = c_int
         lib.actnn_compress_mixed_workspace.argtypes = [c_int64, c_int64, c_int]
         lib.actnn_compress_mixed_workspace.restype = c_int64
+        lib.actnn_calc_precision_workspace.argtypes = []
+        lib.actnn_calc_precision_workspace.restype = c_int64
         lib.actnn_compress_mixed_static_capacity.argtypes = []
         lib.actnn_compress_mixed_static_capacity.restype = c_int64
         _lib = lib

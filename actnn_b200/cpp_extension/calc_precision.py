@@ -28,8 +28,13 @@ def allocate_bits(C: torch.Tensor, initial_bits: int, target: float, w: torch.Te
     offsets = torch.empty(n + 1, dtype=torch.int64, device=C.device) if with_offsets else None
     if w is not None and (not w.is_cuda or w.dtype != torch.int32 or not w.is_contiguous() or w.numel() != n):
         raise RuntimeError("w must be a contiguous int32 CUDA tensor of the same length as C!")
+    # weighted or large problems run as multi-block launches over a small workspace
+    ws = None
+    if not with_offsets and (w is not None or n * (int(initial_bits) - 1) > 8192):
+        ws = torch.empty(256, dtype=torch.uint8, device=C.device)
     _lib.call("actnn_calc_precision", C, C.data_ptr(), _lib.ptr(w), n, int(initial_bits), float(target),
-              bits.data_ptr(), _lib.ptr(offsets), int(num_groups), int(group_size), _lib.stream_of(C))
+              bits.data_ptr(), _lib.ptr(offsets), int(num_groups), int(group_size), _lib.ptr(ws),
+              0 if ws is None else 256, _lib.stream_of(C))
     return bits, offsets
 
 
@@ -45,6 +50,19 @@ def sensitivity(mn: torch.Tensor, mx: torch.Tensor, n: int, range_factor: float,
     _lib.call("actnn_range_sqr", mn, mn.data_ptr(), mx.data_ptr(), n, g, _lib.dtype_id(mn.dtype),
               float(range_factor), float(coeff), _lib.ptr(grad_scale), C.data_ptr(), _lib.stream_of(mn))
     return C
+
+
+def sample_sumsq(grad: torch.Tensor) -> torch.Tensor:
+    """``grad.view(N, -1).float().norm(dim=1).square()`` (actnn/actnn/qscheme.py:50,54) in one
+    read of ``grad``: float32 ``[N]``."""
+    if not grad.is_cuda or grad.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise RuntimeError("grad must be a floating-point CUDA tensor!")
+    grad = grad.contiguous()
+    n = grad.shape[0]
+    out = torch.empty(n, dtype=torch.float32, device=grad.device)
+    _lib.call("actnn_sample_sumsq", grad, grad.data_ptr(), out.data_ptr(), n, grad.numel() // max(n, 1),
+              _lib.dtype_id(grad.dtype), _lib.stream_of(grad))
+    return out
 
 
 def calc_precision(b: torch.Tensor, C: torch.Tensor, w: torch.Tensor, target) -> torch.Tensor:

@@ -58,7 +58,7 @@ extern "C" const char* actnn_status_string(int status) {
   }
 }
 
-extern "C" int actnn_abi_version(void) { return 1; }
+extern "C" int actnn_abi_version(void) { return 2; }
 
 extern "C" int actnn_noise_fill(void* noise, int64_t numel, int dtype, uint64_t seed, uint64_t offset,
                                 actnn_stream_t stream) {

@@ -16,6 +16,15 @@ struct PoolGeom {
   int H, W, Ho, Wo, KH, KW, SH, SW, PH, PW, DH, DW;
 };
 
+// Blocks are persistent: x covers a plane's positions (at most a few blocks), y strides over
+// the planes, and the whole grid is about 16 blocks per SM, so that the cost of launching
+// blocks does not dominate planes of a few thousand positions.
+dim3 plane_grid(int elems_per_plane, int64_t planes) {
+  const int bx = max(1, min(8, (elems_per_plane + 255) / 256));
+  const int64_t by = max((int64_t)1, min(planes, (int64_t)device_info().sm_count * 16 / bx));
+  return dim3((unsigned)bx, (unsigned)by);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 max_pool_forward_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t* __restrict__ idx, int planes,
@@ -50,7 +59,7 @@ max_pool_forward_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t* __re
 template <typename T>
 int launch_forward(const void* x, void* y, int8_t* idx, int64_t planes, const PoolGeom& g, cudaStream_t s) {
   const int out_elems = g.Ho * g.Wo;
-  dim3 grid((unsigned)min(64, (out_elems + 255) / 256), (unsigned)min((int64_t)65535, planes));
+  dim3 grid = plane_grid(out_elems, planes);
   max_pool_forward_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (T*)y, idx, (int)planes, g);
   return check_launch();
 }
@@ -100,7 +109,7 @@ max_pool_backward_kernel(const T* __restrict__ gy, const int8_t* __restrict__ id
 template <typename T>
 int launch_backward(const void* gy, const int8_t* idx, void* gx, int64_t planes, const PoolGeom& g, cudaStream_t s) {
   const int plane_elems = g.H * g.W;
-  dim3 grid((unsigned)min(64, (plane_elems + 255) / 256), (unsigned)min((int64_t)65535, planes));
+  dim3 grid = plane_grid(plane_elems, planes);
   const bool unit = g.DH == 1 && g.DW == 1;
   const int p = (int)planes;
   if (unit && g.SH == 2 && g.SW == 2)

@@ -109,6 +109,52 @@ range_sqr_kernel(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t G
   }
 }
 
+// ---------------------------------------------------------------------------- sample_sumsq
+// Per-sample sum of squares of a gradient [N, F] in float32 (QScheme.set_scale,
+// actnn/actnn/qscheme.py:47-55: grad.view(N, -1).float().norm(dim=1).square()).  One block per
+// sample, vector loads, fixed reduction tree: one read of the gradient, deterministic.
+template <typename T>
+__global__ void __launch_bounds__(512)
+sample_sumsq_kernel(const T* __restrict__ x, float* __restrict__ out, int64_t F, int vector_ok) {
+  __shared__ float partial[16];
+  const T* row = x + (int64_t)blockIdx.x * F;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int64_t octs = vector_ok ? F / kOct : 0;
+  int64_t o = threadIdx.x;
+  for (; o + 3 * 512 < octs; o += 4 * 512) {                    // four independent loads in flight
+    Oct<T> v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = load_oct<T>(row + (o + k * 512) * kOct);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const T* e = reinterpret_cast<const T*>(&v[k]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float f = (float)e[j]; acc[k] = __fmaf_rn(f, f, acc[k]); }
+    }
+  }
+  for (; o < octs; o += 512) {
+    const Oct<T> v = load_oct<T>(row + o * kOct);
+    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float f = (float)e[j]; acc[0] = __fmaf_rn(f, f, acc[0]); }
+  }
+  for (int64_t i = octs * kOct + threadIdx.x; i < F; i += 512) {  // tail, or everything if unaligned
+    const float f = load_scalar<T>(row, i);
+    acc[1] = __fmaf_rn(f, f, acc[1]);
+  }
+  float v = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(kFull, v, s);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tot += partial[i];
+    out[blockIdx.x] = tot;
+  }
+}
+
 // ---------------------------------------------------------------------------- greedy
 // The reference pops a max-heap of (float priority, index) pairs, one bit at a time,
 // until sum(b * w) <= target.  Sample i at width b offers the decrement with priority
@@ -118,8 +164,8 @@ range_sqr_kernel(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t G
 // by (priority desc, index desc, b desc), cut at the first prefix whose weight reaches
 // need = sum(initial * w) - target.  That cut is a weighted selection problem: find the
 // smallest 64-bit key T with weight({key >= T}) >= need; every candidate with key >= T is
-// taken.  T is found bit by bit (64 block-wide counting passes); keys are unique, so ties
-// need no special handling.
+// taken.  T is found four bits per block-wide counting pass; keys are unique, so ties need
+// no special handling.
 struct GreedyCoef { double c[16]; };
 
 ACTNN_DEV uint64_t candidate_key(float C, int w, int b, int64_t i, const GreedyCoef& coef) {
@@ -182,34 +228,62 @@ greedy_kernel(const float* __restrict__ C, const int32_t* __restrict__ w, int64_
     }
   }
 
-  auto weight_at_least = [&](uint64_t thr) -> unsigned long long {
-    unsigned long long s = 0;
-    if (cached) {
-#pragma unroll
-      for (int k = 0; k < kCache; ++k) s += keys[k] >= thr ? wts[k] : 0u;
-    } else {
-      for (int64_t i = tid; i < N; i += kGreedyThreads) {
-        const int wi = WEIGHTED ? w[i] : 1;
-        const float c = C[i];
-        for (int b = initial_bits; b >= 2; --b)
-          s += candidate_key(c, wi, b, i, coef) >= thr ? (unsigned long long)wi : 0ull;
-      }
-    }
-    return s;
-  };
-
   // Largest T with weight({key >= T}) >= need; if even T = 0 falls short every candidate
-  // is taken (the reference's heap would run empty there).
+  // is taken (the reference's heap would run empty there).  Four key bits per block-wide
+  // pass: the weights at or above the 15 trial thresholds T | (j << shift) are summed at
+  // once.  Bits of the low word above those an (index, width) pair can set are skipped.
+  int low_bits = 5;
+  while (((int64_t)1 << (low_bits - 5)) < N) ++low_bits;
+  low_bits = (low_bits + 3) & ~3;
+  __shared__ unsigned long long part15[2][32][15];
   uint64_t T = 0;
   if (need == 0) {
     T = ~0ull;                                                    // nothing is taken (keys < 2^64 - 1)
   } else {
-    int buf = 1;
-    for (int bit = 63; bit >= 0; --bit) {
-      const uint64_t trial = T | (1ull << bit);
-      const unsigned long long got = block_sum(weight_at_least(trial), buf);
+    int buf = 0;
+    for (int shift = 60; shift >= 0; shift -= 4) {
+      if (shift < 32 && shift >= low_bits) continue;
+      unsigned long long sum[15];
+#pragma unroll
+      for (int j = 0; j < 15; ++j) sum[j] = 0;
+      if (cached) {
+#pragma unroll
+        for (int k = 0; k < kCache; ++k) {
+#pragma unroll
+          for (int j = 0; j < 15; ++j) sum[j] += keys[k] >= (T | ((uint64_t)(j + 1) << shift)) ? wts[k] : 0u;
+        }
+      } else {
+        for (int64_t i = tid; i < N; i += kGreedyThreads) {
+          const int wi = WEIGHTED ? w[i] : 1;
+          const float c = C[i];
+          for (int b = initial_bits; b >= 2; --b) {
+            const uint64_t key = candidate_key(c, wi, b, i, coef);
+#pragma unroll
+            for (int j = 0; j < 15; ++j) sum[j] += key >= (T | ((uint64_t)(j + 1) << shift)) ? (unsigned long long)wi : 0ull;
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 15; ++j) {
+#pragma unroll
+        for (int s2 = 16; s2 > 0; s2 >>= 1) sum[j] += __shfl_xor_sync(kFull, sum[j], s2);
+      }
+      if (lane < 15) {
+        unsigned long long mine = 0;
+#pragma unroll
+        for (int j = 0; j < 15; ++j) mine = lane == j ? sum[j] : mine;
+        part15[buf][wid][lane] = mine;
+      }
+      __syncthreads();
+      int digit = 0;
+#pragma unroll
+      for (int j = 0; j < 15; ++j) {
+        unsigned long long tot = 0;
+        for (int w2 = 0; w2 < kGreedyThreads / 32; ++w2) tot += part15[buf][w2][j];
+        if (tot >= need) digit = j + 1;                            // sums fall as j grows
+      }
+      T |= (uint64_t)digit << shift;
       buf ^= 1;
-      if (got >= need) T = trial;
     }
   }
   __syncthreads();
@@ -260,13 +334,14 @@ greedy_kernel(const float* __restrict__ C, const int32_t* __restrict__ w, int64_
 // Fast path for unit weights and few candidates (the per-layer call of every training step):
 // every thread keeps its candidate keys in registers and the threshold is found four bits
 // per block-wide pass (15 trial thresholds at once) instead of one, skipping the bits of
-// the key that are zero for every candidate.  THREADS * kCache keys at most.
-template <int THREADS>
+// the key that are zero for every candidate.  THREADS * KEYS keys at most.
+template <int THREADS, int KEYS>
 __global__ void __launch_bounds__(THREADS)
 greedy_small_kernel(const float* __restrict__ C, int64_t N, int initial_bits, double target, GreedyCoef coef,
                     int32_t* __restrict__ b_out, int64_t* __restrict__ word_offsets, int64_t words_per_bit) {
   constexpr int WARPS = THREADS / 32;
   __shared__ uint32_t part[2][WARPS][8];                       // 15 counts, two per word
+  __shared__ int digit_shared[2];
   __shared__ int scan_sums[WARPS];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int per = initial_bits - 1;
@@ -275,14 +350,16 @@ greedy_small_kernel(const float* __restrict__ C, int64_t N, int initial_bits, do
   const double deficit = (double)b_sum0 - target;
   const int64_t need = deficit > 0.0 ? (int64_t)ceil(deficit) : 0;
 
-  uint64_t keys[kCache];
+  uint32_t key_hi[KEYS], key_lo[KEYS];                         // priority word, (index, width) word
 #pragma unroll
-  for (int k = 0; k < kCache; ++k) {
+  for (int k = 0; k < KEYS; ++k) {
     const int64_t cidx = (int64_t)tid + (int64_t)k * THREADS;
-    keys[k] = 0;                                               // below every real key (b >= 2)
+    key_hi[k] = 0; key_lo[k] = 0;                              // below every real key (b >= 2)
     if (cidx < total) {
       const int64_t i = cidx / per;
-      keys[k] = candidate_key(C[i], 1, initial_bits - (int)(cidx - i * per), i, coef);
+      const uint64_t key = candidate_key(C[i], 1, initial_bits - (int)(cidx - i * per), i, coef);
+      key_hi[k] = (uint32_t)(key >> 32);
+      key_lo[k] = (uint32_t)key;
     }
   }
   // bits of the low word that can be set: (i << 5) | b with i < N
@@ -302,31 +379,42 @@ greedy_small_kernel(const float* __restrict__ C, int64_t N, int initial_bits, do
       uint32_t cnt[8];
 #pragma unroll
       for (int w = 0; w < 8; ++w) cnt[w] = 0;
+      const uint32_t t_hi = (uint32_t)(T >> 32), t_lo = (uint32_t)T;
 #pragma unroll
       for (int j = 1; j < 16; ++j) {
-        const uint64_t trial = T | ((uint64_t)j << shift);
         uint32_t c = 0;
+        if (shift >= 32) {                                     // the trial's low word is zero
+          const uint32_t trial = t_hi | ((uint32_t)j << (shift - 32));
 #pragma unroll
-        for (int k = 0; k < kCache; ++k) c += keys[k] >= trial ? 1u : 0u;
+          for (int k = 0; k < KEYS; ++k) c += key_hi[k] >= trial ? 1u : 0u;
+        } else {                                               // the high word is settled
+          const uint32_t trial = t_lo | ((uint32_t)j << shift);
+#pragma unroll
+          for (int k = 0; k < KEYS; ++k)
+            c += (key_hi[k] > t_hi || (key_hi[k] == t_hi && key_lo[k] >= trial)) ? 1u : 0u;
+        }
         cnt[j >> 1] += c << (16 * (j & 1));
       }
 #pragma unroll
       for (int w = 0; w < 8; ++w) cnt[w] = __reduce_add_sync(kFull, cnt[w]);
       if (lane < 8) part[buf][wid][lane] = cnt[lane];
       __syncthreads();
-      int digit = 0;
-#pragma unroll
-      for (int j = 1; j < 16; ++j) {
+      if (wid == 0) {                                            // lane j totals threshold j over the warps
         uint32_t tot = 0;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) tot += (part[buf][w][j >> 1] >> (16 * (j & 1))) & 0xffffu;
-        if ((int64_t)tot >= need) digit = j;                   // counts fall as j grows
+        if (lane >= 1 && lane < 16) {
+#pragma unroll 4
+          for (int w = 0; w < WARPS; ++w) tot += (part[buf][w][lane >> 1] >> (16 * (lane & 1))) & 0xffffu;
+        }
+        const unsigned ok = __ballot_sync(kFull, lane >= 1 && lane < 16 && (int64_t)tot >= need);
+        if (lane == 0) digit_shared[buf] = 31 - __clz((int)(ok | 1u));   // counts fall as j grows
       }
+      __syncthreads();
+      const int digit = digit_shared[buf];
       T |= (uint64_t)digit << shift;
       buf ^= 1;
     }
   }
-  // widths and word offsets (N <= THREADS * kCache / per, one or more rounds of THREADS)
+  // widths and word offsets, THREADS samples per round
   int carry = 0;
   for (int64_t start = 0; start < N; start += THREADS) {
     const int64_t i = start + tid;
@@ -359,6 +447,105 @@ greedy_small_kernel(const float* __restrict__ C, int64_t N, int initial_bits, do
     }
   }
   if (word_offsets && tid == 0) word_offsets[N] = (int64_t)carry * words_per_bit;
+}
+
+// Large or weighted problems (the once-per-step allocation over layers x samples) with a
+// caller workspace: the same 4-bits-per-pass selection, but every pass is one launch over
+// many blocks.  Blocks add their 15 partial sums to global counters; the block that takes
+// the last ticket of a pass picks the digit and clears the counters for the next pass, so
+// no block ever waits for another.
+struct GreedyState {
+  unsigned long long sums[15];
+  unsigned long long T;
+  unsigned long long need;
+  unsigned long long total_weight;
+  unsigned int ticket;
+  unsigned int pad;
+};
+constexpr int kWsThreads = 256;
+
+__global__ void __launch_bounds__(1024)
+greedy_ws_init_kernel(const int32_t* __restrict__ w, int64_t N, int initial_bits, double target, GreedyState* st) {
+  __shared__ unsigned long long part[32];
+  unsigned long long s = 0;
+  for (int64_t i = threadIdx.x; i < N; i += 1024) s += w ? (unsigned long long)w[i] : 1ull;
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(kFull, s, k);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long tot = 0;
+    for (int k = 0; k < 32; ++k) tot += part[k];
+    const double deficit = (double)(tot * (unsigned long long)initial_bits) - target;
+    for (int j = 0; j < 15; ++j) st->sums[j] = 0;
+    st->total_weight = tot * (unsigned long long)(initial_bits - 1);
+    st->need = deficit > 0.0 ? (unsigned long long)ceil(deficit) : 0ull;
+    st->T = deficit > 0.0 ? 0ull : ~0ull;                        // nothing to take: threshold above every key
+    st->ticket = 0;
+  }
+}
+
+__global__ void __launch_bounds__(kWsThreads)
+greedy_ws_pass_kernel(const float* __restrict__ C, const int32_t* __restrict__ w, int64_t N, int initial_bits,
+                      GreedyCoef coef, int shift, GreedyState* st) {
+  __shared__ unsigned long long part[kWsThreads / 32][15];
+  __shared__ bool last;
+  const unsigned long long T = st->T, need = st->need;
+  if (need == 0 || need >= st->total_weight) return;              // uniform over the grid: nothing to search
+  unsigned long long sum[15];
+#pragma unroll
+  for (int j = 0; j < 15; ++j) sum[j] = 0;
+  for (int64_t i = (int64_t)blockIdx.x * kWsThreads + threadIdx.x; i < N; i += (int64_t)gridDim.x * kWsThreads) {
+    const int wi = w ? w[i] : 1;
+    const float c = C[i];
+    for (int b = initial_bits; b >= 2; --b) {
+      const uint64_t key = candidate_key(c, wi, b, i, coef);
+#pragma unroll
+      for (int j = 0; j < 15; ++j) sum[j] += key >= (T | ((uint64_t)(j + 1) << shift)) ? (unsigned long long)wi : 0ull;
+    }
+  }
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int j = 0; j < 15; ++j) {
+#pragma unroll
+    for (int k = 16; k > 0; k >>= 1) sum[j] += __shfl_xor_sync(kFull, sum[j], k);
+    if (lane == 0) part[wid][j] = sum[j];
+  }
+  __syncthreads();
+  if (threadIdx.x < 15) {
+    unsigned long long tot = 0;
+    for (int k = 0; k < kWsThreads / 32; ++k) tot += part[k][threadIdx.x];
+    if (tot) atomicAdd(&st->sums[threadIdx.x], tot);
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(&st->ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (last && threadIdx.x == 0) {
+    __threadfence();
+    int digit = 0;
+    for (int j = 0; j < 15; ++j) {
+      const unsigned long long v = atomicAdd(&st->sums[j], 0ull);
+      if (v >= need) digit = j + 1;                                // sums fall as j grows
+      st->sums[j] = 0;
+    }
+    st->T = T | ((uint64_t)digit << shift);
+    st->ticket = 0;
+  }
+}
+
+__global__ void __launch_bounds__(kWsThreads)
+greedy_ws_finish_kernel(const float* __restrict__ C, const int32_t* __restrict__ w, int64_t N, int initial_bits,
+                        GreedyCoef coef, const GreedyState* st, int32_t* __restrict__ b_out) {
+  unsigned long long T = st->T;
+  if (st->need != 0 && st->need >= st->total_weight) T = 1;        // every candidate is taken
+  for (int64_t i = (int64_t)blockIdx.x * kWsThreads + threadIdx.x; i < N; i += (int64_t)gridDim.x * kWsThreads) {
+    const int wi = w ? w[i] : 1;
+    const float c = C[i];
+    int b = initial_bits;
+    for (int bb = initial_bits; bb >= 2; --bb) b -= candidate_key(c, wi, bb, i, coef) >= T ? 1 : 0;
+    b_out[i] = b;
+  }
 }
 
 }  // namespace
@@ -408,9 +595,11 @@ extern "C" int actnn_range_sqr(const void* mn, const void* mx, int64_t N, int64_
   return check_launch();
 }
 
+extern "C" int64_t actnn_calc_precision_workspace(void) { return 256; }
+
 extern "C" int actnn_calc_precision(const float* C, const int32_t* w, int64_t N, int initial_bits, double target,
                                     int32_t* b_out, int64_t* word_offsets, int64_t G, int64_t group_size,
-                                    actnn_stream_t stream) {
+                                    void* workspace, int64_t workspace_bytes, actnn_stream_t stream) {
   if (initial_bits < 2 || initial_bits > 15) return ACTNN_ERR_BITS;
   if (N < 0 || N > (1 << 20)) return ACTNN_ERR_SHAPE;
   if (word_offsets && (G < 0 || group_size <= 0 || group_size % 32 != 0)) return ACTNN_ERR_SHAPE;
@@ -432,11 +621,48 @@ extern "C" int actnn_calc_precision(const float* C, const int32_t* w, int64_t N,
   const int64_t wpb = word_offsets ? G * group_size / 32 : 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t candidates = N * (initial_bits - 1);
+  static_assert(sizeof(GreedyState) <= 256, "workspace size");
+  if (workspace && workspace_bytes >= 256 && aligned(workspace, 8) && !word_offsets &&
+      (w || candidates > 1024 * 8)) {
+    // multi-block selection, one launch per four key bits
+    GreedyState* st = (GreedyState*)workspace;
+    int low_bits = 5;
+    while (((int64_t)1 << (low_bits - 5)) < N) ++low_bits;
+    low_bits = (low_bits + 3) & ~3;
+    const int grid = (int)max((int64_t)1, min((N + kWsThreads - 1) / kWsThreads, (int64_t)device_info().sm_count * 4));
+    greedy_ws_init_kernel<<<1, 1024, 0, s>>>(w, N, initial_bits, target, st);
+    for (int shift = 60; shift >= 0; shift -= 4) {
+      if (shift < 32 && shift >= low_bits) continue;
+      greedy_ws_pass_kernel<<<grid, kWsThreads, 0, s>>>(C, w, N, initial_bits, coef, shift, st);
+    }
+    greedy_ws_finish_kernel<<<grid, kWsThreads, 0, s>>>(C, w, N, initial_bits, coef, st, b_out);
+    return check_launch();
+  }
   if (w) greedy_kernel<true><<<1, kGreedyThreads, 0, s>>>(C, w, N, initial_bits, target, coef, b_out, word_offsets, wpb);
-  else if (candidates <= 256 * kCache)
-    greedy_small_kernel<256><<<1, 256, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
-  else if (candidates <= 1024 * kCache)
-    greedy_small_kernel<1024><<<1, 1024, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
+  else if (candidates <= 256 * 8)
+    greedy_small_kernel<256, 8><<<1, 256, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
+  else if (candidates <= 512 * 8)
+    greedy_small_kernel<512, 8><<<1, 512, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
+  else if (candidates <= 1024 * 8)
+    greedy_small_kernel<1024, 8><<<1, 1024, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
   else greedy_kernel<false><<<1, kGreedyThreads, 0, s>>>(C, w, N, initial_bits, target, coef, b_out, word_offsets, wpb);
+  return check_launch();
+}
+
+extern "C" int actnn_sample_sumsq(const void* grad, float* out, int64_t N, int64_t F, int dtype,
+                                  actnn_stream_t stream) {
+  if (N < 0 || F < 0 || N > 0x7fffffff) return ACTNN_ERR_SHAPE;
+  if (N == 0) return ACTNN_OK;
+  if (!grad || !out) return ACTNN_ERR_NULL;
+  if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
+  const size_t al = dtype == ACTNN_F32 ? 32 : 16;
+  const int vector_ok = aligned(grad, al) && (F * dtype_size(dtype)) % al == 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case ACTNN_F32: sample_sumsq_kernel<float><<<(int)N, 512, 0, s>>>((const float*)grad, out, F, vector_ok); break;
+    case ACTNN_F16: sample_sumsq_kernel<__half><<<(int)N, 512, 0, s>>>((const __half*)grad, out, F, vector_ok); break;
+    default:
+      sample_sumsq_kernel<__nv_bfloat16><<<(int)N, 512, 0, s>>>((const __nv_bfloat16*)grad, out, F, vector_ok);
+  }
   return check_launch();
 }

@@ -84,7 +84,7 @@ class QScheme(object):
     def set_scale(self, grad):
         if not QScheme.update_scale:
             return
-        sq = torch.linalg.vector_norm(grad.reshape(grad.shape[0], -1), dim=1, dtype=torch.float32).square()
+        sq = ext_calc_precision.sample_sumsq(grad)
         if config.use_gradient:
             assert QScheme.batch is not None
             self.scales[QScheme.batch] = self.scales[QScheme.batch] * 0.5 + sq.cpu() * 0.5

@@ -332,7 +332,7 @@ def run_ours(args):
             mnx[(r + 4) % POOL][0].data_ptr(), outs[r % 2].data_ptr(), N, G, gs, F16, F16, stream))
         kernels["unpack_mixed_2b_avg"] = {"ms": round(ms, 5), "gbs": round(one_way / ms / 1e6, 1)}
         ms = time_kernel(lambda r: lib.actnn_calc_precision(Cs.data_ptr(), None, N, 8, float(2 * N), bt.data_ptr(),
-                                                           offs.data_ptr(), G, gs, stream))
+                                                           offs.data_ptr(), G, gs, None, 0, stream))
         kernels["calc_precision_n256"] = {"ms": round(ms, 5)}
         del pm, mnx
         masks = [torch.empty((elements + 31) // 32, dtype=torch.int32, device=dev) for _ in range(POOL)]

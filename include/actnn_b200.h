@@ -149,16 +149,27 @@ int actnn_range_sqr(const void* mn, const void* mx, int64_t N, int64_t G, int st
                     float range_factor, float coeff, const float* grad_scale, float* C,
                     actnn_stream_t stream);
 
+/* Per-sample squared gradient norm, out[n] = sum_f float(grad[n, f])^2.
+ * Replaces the torch expression of QScheme.set_scale, actnn/actnn/qscheme.py:47-55
+ * (grad.view(N, -1).float().norm(dim=1).square()) with one read of the gradient. */
+int actnn_sample_sumsq(const void* grad, float* out, int64_t N, int64_t F, int dtype,
+                       actnn_stream_t stream);
+
 /* Replaces: calc_precision(b, C, w, target) -> b,
  * actnn/actnn/cpp_extension/calc_precision.cc:9-50 (a CPU priority queue there; here a
  * weighted radix select over the (initial_bits-1)*N candidate decrements, identical
  * results including tie-breaks).  C[N] float32, w[N] int32 or NULL (all ones),
  * b_out[N] int32, every entry starting from `initial_bits` (2..15).  If word_offsets is
  * not NULL it receives what actnn_bits_prefix would (needs G, group_size).
- * One thread block; N <= 2^20. */
+ * N <= 2^20.  Small unit-weight problems run in one thread block.  `workspace` (optional,
+ * actnn_calc_precision_workspace() bytes, 8-byte aligned, contents unspecified before and
+ * after) lets weighted or large problems without word offsets run as a sequence of
+ * multi-block launches instead of one block; pass NULL / 0 to do without. */
+int64_t actnn_calc_precision_workspace(void);
 int actnn_calc_precision(const float* C, const int32_t* w, int64_t N, int initial_bits,
                          double target, int32_t* b_out, int64_t* word_offsets,
-                         int64_t G, int64_t group_size, actnn_stream_t stream);
+                         int64_t G, int64_t group_size, void* workspace, int64_t workspace_bytes,
+                         actnn_stream_t stream);
 
 /* The adaptive compress of one activation as one call: per-group min/max, sensitivities,
  * greedy allocation at `target` total bits, scale + stochastic rounding + mixed-precision

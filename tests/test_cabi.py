@@ -30,7 +30,7 @@ def test_header_and_binding_agree(lib):
     for name in names:
         assert hasattr(lib, name), "libactnn_b200.so does not export " + name
     bound = set(_lib.SIGNATURES) | {"actnn_status_string", "actnn_abi_version", "actnn_compress_mixed_workspace",
-                                     "actnn_compress_mixed_static_capacity"}
+                                     "actnn_compress_mixed_static_capacity", "actnn_calc_precision_workspace"}
     assert bound == set(names)
 
 
@@ -71,9 +71,9 @@ def test_host_side_validation_needs_no_gpu(lib):
     assert lib.actnn_unpack_mixed(None, None, None, None, None, None, 2, 1, 256, 2, 0, None) == DTYPE
     assert lib.actnn_unpack_single(None, 8, None, None, None, 2, 1, 256, 0, 2, None) == NULL
     # bit allocation
-    assert lib.actnn_calc_precision(None, None, 4, 1, 8.0, None, None, 0, 256, None) == BITS
-    assert lib.actnn_calc_precision(None, None, 4, 8, float("nan"), None, None, 0, 256, None) == ARG
-    assert lib.actnn_calc_precision(None, None, 4, 8, 8.0, None, None, 0, 256, None) == NULL
+    assert lib.actnn_calc_precision(None, None, 4, 1, 8.0, None, None, 0, 256, None, 0, None) == BITS
+    assert lib.actnn_calc_precision(None, None, 4, 8, float("nan"), None, None, 0, 256, None, 0, None) == ARG
+    assert lib.actnn_calc_precision(None, None, 4, 8, 8.0, None, None, 0, 256, None, 0, None) == NULL
     assert lib.actnn_bits_prefix(None, 4, 1, 100, None, None) == NULL
     # mask ops
     assert lib.actnn_relu_forward(None, None, None, -1, 0, None) == SHAPE

@@ -378,3 +378,16 @@ def test_compress_mixed_one_call_equals_stepwise_and_oracle(ext, dtype, shape):
     assert same_values(scale.cpu(), oscale.to(stat)) and same_values(mn.cpu(), omn.to(stat))
     out = ext.q.unpack_mixed_precision(packed, bits, scale, mn, n, g, 256, out_dtype=dtype)
     assert same_values(out.cpu(), O.dequantize(codes, oscale.to(stat).to(dtype), omn.to(stat).to(dtype)))
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("shape", [(16, 64, 28, 28), (3, 1001), (5, 7, 3, 3), (2, 200000)])
+def test_sample_sumsq(ext, dtype, shape):
+    """QScheme.set_scale's per-sample squared gradient norm (qscheme.py:50,54); float
+    accumulation order differs from torch's, hence the relative tolerance 1e-3."""
+    g = make_input(shape, dtype, sum(shape)) * 1e-2
+    got = ext.cp.sample_sumsq(dev(g))
+    ref = g.view(shape[0], -1).float().norm(dim=1).square()
+    assert got.dtype == torch.float32 and torch.allclose(got.cpu(), ref, rtol=1e-3)
+    sliced = dev(g)[1:]                                       # a view that does not start the allocation
+    assert torch.allclose(ext.cp.sample_sumsq(sliced).cpu(), ref[1:], rtol=1e-3)
