@@ -44,6 +44,8 @@ SIGNATURES = {
     "actnn_max_pool2d_forward": [_P, _P, _P, _L, _L, _L, _L] + [_I] * 9 + [_P],
     "actnn_max_pool2d_backward": [_P, _P, _P, _L, _L, _L, _L] + [_I] * 9 + [_P],
     "actnn_noise_fill": [_P, _L, _I, _U, _U, _P],
+    "actnn_batch_norm_forward": [_P] * 8 + [_L, _L, _L, _D, _D, _I, _P, _L, _P],
+    "actnn_batch_norm_backward": [_P] * 8 + [_L, _L, _L, _I, _P, _L, _P],
 }
 
 _lib = None
@@ -70,6 +72,8 @@ def load() -> ctypes.CDLL:
         lib.actnn_compress_mixed_workspace.restype = c_int64
         lib.actnn_calc_precision_workspace.argtypes = []
         lib.actnn_calc_precision_workspace.restype = c_int64
+        lib.actnn_batch_norm_workspace.argtypes = [c_int64, c_int64, c_int64]
+        lib.actnn_batch_norm_workspace.restype = c_int64
         lib.actnn_compress_mixed_static_capacity.argtypes = []
         lib.actnn_compress_mixed_static_capacity.restype = c_int64
         _lib = lib

@@ -1,11 +1,17 @@
-"""ATen backward operators under the names the reference re-exports
+"""Backward operators under the names the reference re-exports
 (actnn/actnn/cpp_extension/backward_func.cc:81-91).
 
 PyTorch 2.x dropped ``cudnn_convolution_backward`` / ``cudnn_convolution_transpose_backward``
 in favour of ``convolution_backward``; the two names are kept here with the reference's
-argument order and are routed to that operator.  The dense math stays in cuDNN / ATen: this
-module holds no kernels."""
+argument order and are routed to that operator: the dense convolution math stays in cuDNN.
+
+``cudnn_batch_norm`` / ``cudnn_batch_norm_backward`` keep the reference's names, arguments
+and return values, but the training-mode work is done by this package's own kernels
+(``actnn_batch_norm_forward`` / ``actnn_batch_norm_backward`` of the C ABI), which spread a
+channel over many blocks instead of cuDNN's one block per channel."""
 import torch
+
+from .. import _lib
 
 aten = torch.ops.aten
 
@@ -37,16 +43,72 @@ def cudnn_convolution_transpose_backward(input, grad_output, weight, padding, ou
     return gi, gw
 
 
+def _as_f32(t):
+    return None if t is None else (t if t.dtype == torch.float32 else t.float()).contiguous()
+
+
+def _bn_dims(input):
+    if input.dim() < 2:
+        raise RuntimeError("batch_norm: expected an input of at least 2 dimensions, got %d" % input.dim())
+    N, C = input.shape[0], input.shape[1]
+    HW = input.numel() // (N * C) if N * C else 0
+    return N, C, HW
+
+
+def _bn_workspace(N, C, HW, device):
+    nbytes = _lib.load().actnn_batch_norm_workspace(N, C, HW)
+    return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device), nbytes
+
+
 def cudnn_batch_norm(input, weight, bias, running_mean, running_var, training, exponential_average_factor,
                      epsilon):
-    return aten.cudnn_batch_norm(input, weight, bias, running_mean, running_var, training,
-                                 exponential_average_factor, epsilon)
+    """Returns ``(output, save_mean, save_invstd, reserve)`` like ``at::cudnn_batch_norm``
+    (reference call site: ops.py:457-458).  ``reserve`` is an empty byte tensor."""
+    if not training:
+        return aten.cudnn_batch_norm(input, weight, bias, running_mean, running_var, training,
+                                     exponential_average_factor, epsilon)
+    if not input.is_cuda:
+        raise RuntimeError("cudnn_batch_norm: the input must be a CUDA tensor")
+    x = input.contiguous()
+    N, C, HW = _bn_dims(x)
+    w32, b32 = _as_f32(weight), _as_f32(bias)
+    for name, t in (("running_mean", running_mean), ("running_var", running_var)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise RuntimeError("cudnn_batch_norm: %s must be a contiguous float32 tensor" % name)
+    y = torch.empty_like(x)
+    save_mean = torch.empty(C, dtype=torch.float32, device=x.device)
+    save_invstd = torch.empty(C, dtype=torch.float32, device=x.device)
+    ws, nbytes = _bn_workspace(N, C, HW, x.device)
+    _lib.call("actnn_batch_norm_forward", x, _lib.ptr(x), _lib.ptr(w32), _lib.ptr(b32), _lib.ptr(running_mean),
+              _lib.ptr(running_var), _lib.ptr(y), _lib.ptr(save_mean), _lib.ptr(save_invstd), N, C, HW,
+              float(exponential_average_factor), float(epsilon), _lib.dtype_id(x.dtype), _lib.ptr(ws), nbytes,
+              _lib.stream_of(x))
+    return y, save_mean, save_invstd, torch.empty(0, dtype=torch.uint8, device=x.device)
 
 
 def cudnn_batch_norm_backward(input, grad_output, weight, running_mean, running_var, save_mean, save_var,
                               epsilon, reserve):
-    return aten.cudnn_batch_norm_backward(input, grad_output, weight, running_mean, running_var, save_mean,
-                                          save_var, epsilon, reserve)
+    """Returns ``(grad_input, grad_weight, grad_bias)`` like ``at::cudnn_batch_norm_backward``
+    (reference call site: ops.py:492-493); ``save_var`` is the inverse standard deviation the
+    forward saved."""
+    if not input.is_cuda:
+        raise RuntimeError("cudnn_batch_norm_backward: the input must be a CUDA tensor")
+    x = input.contiguous()
+    dy = grad_output.contiguous()
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    N, C, HW = _bn_dims(x)
+    w32 = _as_f32(weight)
+    dx = torch.empty_like(x)
+    dweight = torch.empty(C, dtype=torch.float32, device=x.device)
+    dbias = torch.empty(C, dtype=torch.float32, device=x.device)
+    ws, nbytes = _bn_workspace(N, C, HW, x.device)
+    _lib.call("actnn_batch_norm_backward", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(w32), _lib.ptr(save_mean),
+              _lib.ptr(save_var), _lib.ptr(dx), _lib.ptr(dweight), _lib.ptr(dbias), N, C, HW,
+              _lib.dtype_id(x.dtype), _lib.ptr(ws), nbytes, _lib.stream_of(x))
+    if weight is not None and weight.dtype != torch.float32:
+        dweight, dbias = dweight.to(weight.dtype), dbias.to(weight.dtype)
+    return dx, dweight, dbias
 
 
 def native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps):

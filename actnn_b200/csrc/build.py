@@ -14,7 +14,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["api.cu", "codec_mixed.cu", "codec_single.cu", "compress_mixed.cu", "stats.cu", "mask_ops.cu",
-           "maxpool.cu"]
+           "maxpool.cu", "batch_norm.cu"]
 HEADERS = ["common.cuh", "quant_math.cuh", os.path.join("..", "..", "include", "actnn_b200.h")]
 LIB = os.path.join(HERE, "libactnn_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

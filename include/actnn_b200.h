@@ -256,6 +256,32 @@ int actnn_max_pool2d_backward(const void* grad_out, const int8_t* idx, void* gra
                               actnn_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * Training-mode batch normalisation of an NCHW tensor viewed as [N, C, HW] (HW = 1 for a
+ * [N, C] input).  Replaces the cuDNN calls the reference's quantized batch-norm operator
+ * makes: ext_backward_func.cudnn_batch_norm / cudnn_batch_norm_backward, re-exported at
+ * actnn/actnn/cpp_extension/backward_func.cc:87-88 and called at actnn/actnn/ops.py:457-458
+ * and actnn/actnn/ops.py:492-493.  Same results (batch statistics with the biased variance,
+ * running statistics updated with `momentum` and the unbiased variance, save_mean and
+ * save_invstd = 1/sqrt(var + eps) for backward); statistics, weight, bias and their
+ * gradients are float32 whatever `dtype` is.  weight / bias NULL mean 1 / 0;
+ * running_mean / running_var NULL skip the update; grad_in / grad_weight / grad_bias NULL
+ * skip that output.  `workspace` holds per-channel partial sums:
+ * actnn_batch_norm_workspace(N, C, HW) bytes for the current device, 16-byte aligned, its
+ * contents need not be kept between calls.  Sums are added in a fixed order, so equal
+ * inputs give equal bits. */
+int64_t actnn_batch_norm_workspace(int64_t N, int64_t C, int64_t HW);
+int actnn_batch_norm_forward(const void* x, const float* weight, const float* bias,
+                             float* running_mean, float* running_var, void* y, float* save_mean,
+                             float* save_invstd, int64_t N, int64_t C, int64_t HW, double momentum,
+                             double eps, int dtype, void* workspace, int64_t workspace_bytes,
+                             actnn_stream_t stream);
+int actnn_batch_norm_backward(const void* x, const void* grad_out, const float* weight,
+                              const float* save_mean, const float* save_invstd, void* grad_in,
+                              float* grad_weight, float* grad_bias, int64_t N, int64_t C, int64_t HW,
+                              int dtype, void* workspace, int64_t workspace_bytes,
+                              actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * The rounding noise the pack kernels draw for (seed, offset) when `noise == NULL`,
  * written as a [numel] array of `dtype` indexed like the padded [N, G, 256] activation.
  * No counterpart in the reference (it draws cuRAND numbers it cannot replay); exists so

@@ -464,6 +464,46 @@ def max_pool2d_backward(grad: torch.Tensor, idx: torch.Tensor, input_shape, kern
 # --------------------------------------------------------------------------------------
 # noise
 # --------------------------------------------------------------------------------------
+def batch_norm_forward(x: torch.Tensor, weight, bias, running_mean, running_var, momentum: float, eps: float):
+    """Training-mode batch norm in float64: what ``cudnn_batch_norm`` computes at the
+    reference's call site (ops.py:457-458).  Returns ``(y, save_mean, save_invstd,
+    new_running_mean, new_running_var)``; y is rounded to x's dtype, the rest is float64."""
+    C = x.shape[1]
+    x64 = x.double().transpose(0, 1).reshape(C, -1)
+    M = x64.shape[1]
+    mean = x64.mean(dim=1)
+    var = ((x64 - mean[:, None]) ** 2).mean(dim=1)
+    invstd = 1.0 / torch.sqrt(var + eps)
+    w = torch.ones(C, dtype=torch.float64) if weight is None else weight.double()
+    b = torch.zeros(C, dtype=torch.float64) if bias is None else bias.double()
+    shape = [1, C] + [1] * (x.dim() - 2)
+    y = (x.double() - mean.view(shape)) * (invstd * w).view(shape) + b.view(shape)
+    new_rm = new_rv = None
+    if running_mean is not None:
+        new_rm = (1 - momentum) * running_mean.double() + momentum * mean
+    if running_var is not None:
+        unbiased = var * (M / (M - 1)) if M > 1 else var
+        new_rv = (1 - momentum) * running_var.double() + momentum * unbiased
+    return y.to(x.dtype), mean, invstd, new_rm, new_rv
+
+
+def batch_norm_backward(x: torch.Tensor, grad_out: torch.Tensor, weight, save_mean, save_invstd):
+    """Gradients of training-mode batch norm in float64 (``cudnn_batch_norm_backward``,
+    reference call site ops.py:492-493): ``(grad_input, grad_weight, grad_bias)``."""
+    C = x.shape[1]
+    shape = [1, C] + [1] * (x.dim() - 2)
+    dims = [d for d in range(x.dim()) if d != 1]
+    M = x.numel() // C
+    mean, invstd = save_mean.double().view(shape), save_invstd.double().view(shape)
+    w = torch.ones(C, dtype=torch.float64) if weight is None else weight.double()
+    g = grad_out.double()
+    xhat = (x.double() - mean) * invstd
+    sum_dy = g.sum(dim=dims)
+    sum_dy_xhat = (g * xhat).sum(dim=dims)
+    dx = (w * save_invstd.double()).view(shape) * (g - sum_dy.view(shape) / M - xhat * sum_dy_xhat.view(shape) / M)
+    return dx.to(x.dtype), sum_dy_xhat, sum_dy
+
+
 def torch_noise(shape, dtype, generator: Optional[torch.Generator] = None) -> torch.Tensor:
     """``output.new(shape).uniform_(-0.5, 0.5)`` (ops.py:37) from a CPU generator."""
     return torch.empty(shape, dtype=dtype).uniform_(-0.5, 0.5, generator=generator)

@@ -1,0 +1,119 @@
+"""The batch-norm kernels behind ``cudnn_batch_norm`` / ``cudnn_batch_norm_backward`` against
+the float64 oracle (GPU)."""
+import pytest
+import torch
+
+import actnn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+# tolerance: outputs are rounded once to the tensor dtype from float32 arithmetic
+TOL = {torch.float32: 2e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}
+
+SHAPES = [
+    (8, 64, 56, 56),     # 16-byte vectors, several splits per channel
+    (16, 32, 14, 14),    # 196 positions: 8-byte vectors for 16-bit types
+    (16, 48, 7, 7),      # 49 positions: scalar path
+    (3, 5, 6, 10),       # ragged everything
+    (64, 10),            # [N, C]
+    (4, 6, 33),          # [N, C, L]
+    (1, 8, 16, 16),      # one sample
+    (32, 300, 4, 4),     # more channels than blocks wanted: one split
+]
+
+
+def _inputs(shape, dtype, dev, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    C = shape[1]
+    x = (torch.randn(shape, generator=g) * 1.7 + torch.linspace(-3, 3, C).view([1, C] + [1] * (len(shape) - 2)))
+    gy = torch.randn(shape, generator=g)
+    w, b = torch.randn(C, generator=g), torch.randn(C, generator=g)
+    rm, rv = torch.randn(C, generator=g), torch.rand(C, generator=g) + 0.5
+    return x.to(dtype).to(dev), gy.to(dtype).to(dev), w.to(dev), b.to(dev), rm.to(dev), rv.to(dev)
+
+
+def _close(got, want, tol):
+    want = want.to(got.device)
+    scale = max(1.0, float(want.abs().max()))
+    return float((got.double() - want.double()).abs().max()) <= tol * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_batch_norm_forward_backward(cuda_device, shape, dtype):
+    from actnn_b200.cpp_extension import backward_func as bf
+    x, gy, w, b, rm, rv = _inputs(shape, dtype, cuda_device)
+    rm0, rv0 = rm.clone(), rv.clone()
+    y, mean, invstd, reserve = bf.cudnn_batch_norm(x, w, b, rm, rv, True, 0.1, 1e-5)
+    y_o, mean_o, invstd_o, rm_o, rv_o = O.batch_norm_forward(x.cpu(), w.cpu(), b.cpu(), rm0.cpu(), rv0.cpu(), 0.1, 1e-5)
+    tol = TOL[dtype]
+    assert y.dtype == dtype and y.shape == x.shape and reserve.numel() == 0
+    assert _close(y, y_o, tol)
+    assert _close(mean, mean_o, 1e-5) and _close(invstd, invstd_o, 1e-4)
+    assert _close(rm, rm_o, 1e-5) and _close(rv, rv_o, 1e-5)
+    dx, dw, db = bf.cudnn_batch_norm_backward(x, gy, w, rm, rv, mean, invstd, 1e-5, reserve)
+    dx_o, dw_o, db_o = O.batch_norm_backward(x.cpu(), gy.cpu(), w.cpu(), mean.cpu(), invstd.cpu())
+    assert dx.dtype == dtype and _close(dx, dx_o, tol)
+    assert _close(dw, dw_o, 1e-4) and _close(db, db_o, 1e-4)
+
+
+def test_batch_norm_matches_cudnn_and_is_deterministic(cuda_device):
+    """Against the operator the reference calls, and bit-equal on a second run."""
+    from actnn_b200.cpp_extension import backward_func as bf
+    x, gy, w, b, rm, rv = _inputs((32, 64, 28, 28), torch.float16, cuda_device, seed=3)
+    rm_t, rv_t = rm.clone(), rv.clone()
+    y_t, mean_t, invstd_t, res_t = torch.ops.aten.cudnn_batch_norm(x, w, b, rm_t, rv_t, True, 0.1, 1e-5)
+    dx_t, dw_t, db_t = torch.ops.aten.cudnn_batch_norm_backward(x, gy, w, rm_t, rv_t, mean_t, invstd_t, 1e-5, res_t)
+    rm1, rv1 = rm.clone(), rv.clone()
+    y, mean, invstd, res = bf.cudnn_batch_norm(x, w, b, rm1, rv1, True, 0.1, 1e-5)
+    dx, dw, db = bf.cudnn_batch_norm_backward(x, gy, w, rm1, rv1, mean, invstd, 1e-5, res)
+    assert _close(y, y_t, 2e-3) and _close(dx, dx_t, 2e-3)
+    assert _close(mean, mean_t, 1e-5) and _close(invstd, invstd_t, 1e-4)
+    assert _close(rm1, rm_t, 1e-5) and _close(rv1, rv_t, 1e-5)
+    assert _close(dw, dw_t, 2e-4) and _close(db, db_t, 2e-4)
+    rm2, rv2 = rm.clone(), rv.clone()
+    y2, mean2, invstd2, _ = bf.cudnn_batch_norm(x, w, b, rm2, rv2, True, 0.1, 1e-5)
+    dx2, dw2, db2 = bf.cudnn_batch_norm_backward(x, gy, w, rm2, rv2, mean2, invstd2, 1e-5, res)
+    for a, c in ((y, y2), (mean, mean2), (invstd, invstd2), (dx, dx2), (dw, dw2), (db, db2), (rm1, rm2)):
+        assert torch.equal(a, c)
+
+
+def test_batch_norm_large_offset_variance(cuda_device):
+    """A mean far above the deviation: the shifted sums keep the variance."""
+    from actnn_b200.cpp_extension import backward_func as bf
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(16, 8, 32, 32, generator=g) * 0.01 + 100.0).to(cuda_device)
+    y, mean, invstd, _ = bf.cudnn_batch_norm(x, None, None, None, None, True, 0.1, 1e-5)
+    _, mean_o, invstd_o, _, _ = O.batch_norm_forward(x.cpu(), None, None, None, None, 0.1, 1e-5)
+    assert _close(invstd, invstd_o, 1e-3) and _close(mean, mean_o, 1e-6)
+
+
+@pytest.fixture()
+def actnn(cuda_device):
+    import actnn_b200
+    from actnn_b200.conf import QuantizationConfig
+    fresh = QuantizationConfig()
+    actnn_b200.config.__dict__.update(fresh.__dict__)
+    yield actnn_b200
+    actnn_b200.config.__dict__.update(fresh.__dict__)
+
+
+def test_batch_norm_module_trains_like_torch(actnn, cuda_device):
+    """QBatchNorm2d at level L0 (no compression) against nn.BatchNorm2d."""
+    actnn.set_optimization_level("L0")
+    torch.manual_seed(0)
+    ref = torch.nn.BatchNorm2d(24).to(cuda_device)
+    ours = actnn.QBatchNorm2d(24).to(cuda_device)
+    ours.load_state_dict(ref.state_dict())
+    x = torch.randn(8, 24, 12, 12, device=cuda_device)
+    xr, xo = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    yr, yo = ref(xr), ours(xo)
+    gy = torch.randn_like(yr)
+    yr.backward(gy)
+    yo.backward(gy)
+    assert torch.allclose(yo, yr, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(xo.grad, xr.grad, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(ours.weight.grad, ref.weight.grad, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(ours.bias.grad, ref.bias.grad, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(ours.running_var, ref.running_var, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(ours.running_mean, ref.running_mean, rtol=1e-5, atol=1e-6)

@@ -152,3 +152,25 @@ def test_relu_and_maxpool_oracle_agree_with_torch():
         go = torch.randn(ref.shape, generator=g)
         ref.backward(go)
         assert torch.allclose(O.max_pool2d_backward(go, idx, x.shape, k, s, p), xr.grad, atol=1e-6)
+
+
+# ------------------------------------------------------------------ batch norm
+@pytest.mark.parametrize("shape", [(4, 3, 5, 7), (6, 5), (2, 4, 9)])
+def test_batch_norm_oracle_matches_torch_cpu(shape):
+    """The float64 restatement against PyTorch's own CPU batch norm and its autograd."""
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(shape, generator=g, dtype=torch.float64) * 2 + 3).requires_grad_(True)
+    C = shape[1]
+    w = torch.randn(C, generator=g, dtype=torch.float64).requires_grad_(True)
+    b = torch.randn(C, generator=g, dtype=torch.float64).requires_grad_(True)
+    rm, rv = torch.randn(C, generator=g, dtype=torch.float64), torch.rand(C, generator=g, dtype=torch.float64) + 0.5
+    rm_t, rv_t = rm.clone(), rv.clone()
+    y_t = torch.nn.functional.batch_norm(x, rm_t, rv_t, w, b, True, 0.1, 1e-5)
+    gy = torch.randn(shape, generator=g, dtype=torch.float64)
+    gx_t, gw_t, gb_t = torch.autograd.grad(y_t, (x, w, b), gy)
+    y, mean, invstd, new_rm, new_rv = O.batch_norm_forward(x.detach(), w.detach(), b.detach(), rm, rv, 0.1, 1e-5)
+    assert torch.allclose(y, y_t, rtol=1e-10, atol=1e-10)
+    assert torch.allclose(new_rm, rm_t, rtol=1e-10, atol=1e-12) and torch.allclose(new_rv, rv_t, rtol=1e-10, atol=1e-12)
+    gx, gw, gb = O.batch_norm_backward(x.detach(), gy, w.detach(), mean, invstd)
+    assert torch.allclose(gx, gx_t, rtol=1e-9, atol=1e-10)
+    assert torch.allclose(gw, gw_t, rtol=1e-9, atol=1e-10) and torch.allclose(gb, gb_t, rtol=1e-9, atol=1e-10)
