@@ -331,122 +331,158 @@ greedy_kernel(const float* __restrict__ C, const int32_t* __restrict__ w, int64_
   if (word_offsets && tid == 0) word_offsets[N] = carry * words_per_bit;
 }
 
-// Fast path for unit weights and few candidates (the per-layer call of every training step):
-// every thread keeps its candidate keys in registers and the threshold is found four bits
-// per block-wide pass (15 trial thresholds at once) instead of one, skipping the bits of
-// the key that are zero for every candidate.  THREADS * KEYS keys at most.
-template <int THREADS, int KEYS>
+// Fast path for unit weights and at most THREADS samples (the per-layer call of every
+// training step): thread i owns sample i and keeps its initial_bits - 1 candidate keys in
+// registers, so nothing is recomputed and nothing but C is read.  The priority word is
+// selected first, four bits per block-wide pass (15 trial thresholds at once, one barrier
+// per pass); the (index, width) word is searched only when several candidates share the
+// boundary priority.
+template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
-greedy_small_kernel(const float* __restrict__ C, int64_t N, int initial_bits, double target, GreedyCoef coef,
-                    int32_t* __restrict__ b_out, int64_t* __restrict__ word_offsets, int64_t words_per_bit) {
+greedy_sample_kernel(const float* __restrict__ C, int N, int initial_bits, double target, GreedyCoef coef,
+                     int32_t* __restrict__ b_out, int64_t* __restrict__ word_offsets, int64_t words_per_bit) {
   constexpr int WARPS = THREADS / 32;
-  __shared__ uint32_t part[2][WARPS][8];                       // 15 counts, two per word
-  __shared__ int digit_shared[2];
+  constexpr int KEYS = 8;                                      // widths initial_bits .. 2, initial_bits <= 9
+  __shared__ uint32_t part[2][WARPS][8];                       // 15 counts of 16 bits, two per word
   __shared__ int scan_sums[WARPS];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int per = initial_bits - 1;
-  const int64_t total = N * per;
-  const int64_t b_sum0 = N * initial_bits;
-  const double deficit = (double)b_sum0 - target;
-  const int64_t need = deficit > 0.0 ? (int64_t)ceil(deficit) : 0;
+  const int total = N * per;
+  const double deficit = (double)N * (double)initial_bits - target;
+  const int64_t need64 = deficit > 0.0 ? (int64_t)ceil(deficit) : 0;
+  const int need = (int)min(need64, (int64_t)total + 1);
 
-  uint32_t key_hi[KEYS], key_lo[KEYS];                         // priority word, (index, width) word
+  uint32_t key_hi[KEYS], key_lo[KEYS];                         // priority word; (index << 4) | width
 #pragma unroll
-  for (int k = 0; k < KEYS; ++k) {
-    const int64_t cidx = (int64_t)tid + (int64_t)k * THREADS;
-    key_hi[k] = 0; key_lo[k] = 0;                              // below every real key (b >= 2)
-    if (cidx < total) {
-      const int64_t i = cidx / per;
-      const uint64_t key = candidate_key(C[i], 1, initial_bits - (int)(cidx - i * per), i, coef);
-      key_hi[k] = (uint32_t)(key >> 32);
-      key_lo[k] = (uint32_t)key;
+  for (int k = 0; k < KEYS; ++k) { key_hi[k] = 0; key_lo[k] = 0; }   // below every real key
+  if (tid < N) {
+    const double c = (double)C[tid];
+#pragma unroll
+    for (int k = 0; k < KEYS; ++k) {
+      const int b = initial_bits - k;
+      if (k < per) {
+        float p = (float)(c * coef.c[b]);
+        if (p == 0.f) p = 0.f;
+        const uint32_t u = __float_as_uint(p);
+        key_hi[k] = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        key_lo[k] = ((uint32_t)tid << 4) | (uint32_t)b;
+      }
     }
   }
-  // bits of the low word that can be set: (i << 5) | b with i < N
-  int low_bits = 5;
-  while (((int64_t)1 << (low_bits - 5)) < N) ++low_bits;
-  low_bits = (low_bits + 3) & ~3;
 
-  uint64_t T = 0;
+  // Sums the 15 packed counts over the block; returns the largest j whose count reaches
+  // `want` (0 if none).  Counts fall as j grows.
+  int buf = 0;
+  auto pick_digit = [&](uint32_t (&cnt)[8], int want) -> int {
+#pragma unroll
+    for (int w = 0; w < 8; ++w) cnt[w] = __reduce_add_sync(kFull, cnt[w]);
+    if (lane < 8) part[buf][wid][lane] = cnt[lane];
+    __syncthreads();
+    const int j = lane & 15, half = lane >> 4;
+    uint32_t tot = 0;
+    if (WARPS == 1) {
+      tot = half == 0 ? (part[buf][0][j >> 1] >> (16 * (j & 1))) & 0xffffu : 0u;
+    } else {
+#pragma unroll
+      for (int w = 0; w < WARPS / 2; ++w)
+        tot += (part[buf][half * (WARPS / 2) + w][j >> 1] >> (16 * (j & 1))) & 0xffffu;
+    }
+    tot += __shfl_xor_sync(kFull, tot, 16);
+    const unsigned ok = __ballot_sync(kFull, lane >= 1 && lane < 16 && (int)tot >= want);
+    buf ^= 1;
+    return 31 - __clz((int)(ok | 1u));
+  };
+
+  uint32_t T_hi = 0, T_lo = 0;
   if (need == 0) {
-    T = ~0ull;
+    T_hi = ~0u; T_lo = ~0u;                                     // nothing is taken
   } else if (need >= total) {
-    T = 1;                                                     // every candidate is taken
+    T_hi = 0; T_lo = 1;                                         // every candidate is taken
   } else {
-    int buf = 0;
-    for (int shift = 60; shift >= 0; shift -= 4) {
-      if (shift < 32 && shift >= low_bits) continue;           // always-zero key bits
+    for (int shift = 28; shift >= 0; shift -= 4) {
       uint32_t cnt[8];
 #pragma unroll
       for (int w = 0; w < 8; ++w) cnt[w] = 0;
-      const uint32_t t_hi = (uint32_t)(T >> 32), t_lo = (uint32_t)T;
 #pragma unroll
       for (int j = 1; j < 16; ++j) {
+        const uint32_t trial = T_hi | ((uint32_t)j << shift);
         uint32_t c = 0;
-        if (shift >= 32) {                                     // the trial's low word is zero
-          const uint32_t trial = t_hi | ((uint32_t)j << (shift - 32));
 #pragma unroll
-          for (int k = 0; k < KEYS; ++k) c += key_hi[k] >= trial ? 1u : 0u;
-        } else {                                               // the high word is settled
-          const uint32_t trial = t_lo | ((uint32_t)j << shift);
-#pragma unroll
-          for (int k = 0; k < KEYS; ++k)
-            c += (key_hi[k] > t_hi || (key_hi[k] == t_hi && key_lo[k] >= trial)) ? 1u : 0u;
-        }
+        for (int k = 0; k < KEYS; ++k) c += key_hi[k] >= trial ? 1u : 0u;
         cnt[j >> 1] += c << (16 * (j & 1));
       }
+      T_hi |= (uint32_t)pick_digit(cnt, need) << shift;
+    }
+    // candidates above the boundary priority, and those on it
+    uint32_t above = 0, on = 0;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) cnt[w] = __reduce_add_sync(kFull, cnt[w]);
-      if (lane < 8) part[buf][wid][lane] = cnt[lane];
-      __syncthreads();
-      if (wid == 0) {                                            // lane j totals threshold j over the warps
-        uint32_t tot = 0;
-        if (lane >= 1 && lane < 16) {
-#pragma unroll 4
-          for (int w = 0; w < WARPS; ++w) tot += (part[buf][w][lane >> 1] >> (16 * (lane & 1))) & 0xffffu;
+    for (int k = 0; k < KEYS; ++k) {
+      above += key_hi[k] > T_hi ? 1u : 0u;
+      on += key_hi[k] == T_hi ? 1u : 0u;
+    }
+    uint32_t both = __reduce_add_sync(kFull, above | (on << 16));
+    if (lane == 0) part[buf][wid][0] = both;
+    __syncthreads();
+    both = 0;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) both += part[buf][w][0];
+    buf ^= 1;
+    const int n_above = (int)(both & 0xffffu), n_on = (int)(both >> 16);
+    const int need_lo = need - n_above;                         // 1 .. n_on
+    if (need_lo >= n_on) {
+      T_lo = 0;                                                 // the whole tie is taken
+    } else {
+      int low_bits = 4;
+      while ((1 << (low_bits - 4)) < N) ++low_bits;
+      low_bits = (low_bits + 3) & ~3;
+      uint32_t tied[KEYS];
+#pragma unroll
+      for (int k = 0; k < KEYS; ++k) tied[k] = key_hi[k] == T_hi ? key_lo[k] : 0u;
+      for (int shift = low_bits - 4; shift >= 0; shift -= 4) {
+        uint32_t cnt[8];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) cnt[w] = 0;
+#pragma unroll
+        for (int j = 1; j < 16; ++j) {
+          const uint32_t trial = T_lo | ((uint32_t)j << shift);
+          uint32_t c = 0;
+#pragma unroll
+          for (int k = 0; k < KEYS; ++k) c += tied[k] >= trial ? 1u : 0u;
+          cnt[j >> 1] += c << (16 * (j & 1));
         }
-        const unsigned ok = __ballot_sync(kFull, lane >= 1 && lane < 16 && (int64_t)tot >= need);
-        if (lane == 0) digit_shared[buf] = 31 - __clz((int)(ok | 1u));   // counts fall as j grows
+        T_lo |= (uint32_t)pick_digit(cnt, need_lo) << shift;
       }
-      __syncthreads();
-      const int digit = digit_shared[buf];
-      T |= (uint64_t)digit << shift;
-      buf ^= 1;
     }
   }
-  // widths and word offsets, THREADS samples per round
-  int carry = 0;
-  for (int64_t start = 0; start < N; start += THREADS) {
-    const int64_t i = start + tid;
-    int b = 0;
-    if (i < N) {
-      const float c = C[i];
-      b = initial_bits;
-      for (int bb = initial_bits; bb >= 2; --bb) b -= candidate_key(c, 1, bb, i, coef) >= T ? 1 : 0;
-      b_out[i] = b;
-    }
-    if (word_offsets) {
-      int incl = b;
+
+  int b = 0;
+  if (tid < N) {
+    b = initial_bits;
 #pragma unroll
-      for (int s = 1; s < 32; s <<= 1) {
-        const int t = __shfl_up_sync(kFull, incl, s);
-        if (lane >= s) incl += t;
-      }
-      __syncthreads();
-      if (lane == 31) scan_sums[wid] = incl;
-      __syncthreads();
-      int before = 0, block_total = 0;
-#pragma unroll
-      for (int w = 0; w < WARPS; ++w) {
-        const int v = scan_sums[w];
-        before += w < wid ? v : 0;
-        block_total += v;
-      }
-      if (i < N) word_offsets[i] = (int64_t)(carry + before + incl - b) * words_per_bit;
-      carry += block_total;
-    }
+    for (int k = 0; k < KEYS; ++k)
+      b -= (k < per && (key_hi[k] > T_hi || (key_hi[k] == T_hi && key_lo[k] >= T_lo))) ? 1 : 0;
+    b_out[tid] = b;
   }
-  if (word_offsets && tid == 0) word_offsets[N] = (int64_t)carry * words_per_bit;
+  if (word_offsets) {
+    int incl = b;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const int t = __shfl_up_sync(kFull, incl, s);
+      if (lane >= s) incl += t;
+    }
+    __syncthreads();
+    if (lane == 31) scan_sums[wid] = incl;
+    __syncthreads();
+    int before = 0, block_total = 0;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const int v = scan_sums[w];
+      before += w < wid ? v : 0;
+      block_total += v;
+    }
+    if (tid < N) word_offsets[tid] = (int64_t)(before + incl - b) * words_per_bit;
+    if (tid == 0) word_offsets[N] = (int64_t)block_total * words_per_bit;
+  }
 }
 
 // Large or weighted problems (the once-per-step allocation over layers x samples) with a
@@ -638,13 +674,20 @@ extern "C" int actnn_calc_precision(const float* C, const int32_t* w, int64_t N,
     greedy_ws_finish_kernel<<<grid, kWsThreads, 0, s>>>(C, w, N, initial_bits, coef, st, b_out);
     return check_launch();
   }
+  if (!w && N <= 1024 && initial_bits <= 9) {
+    const int n = (int)N;
+#define ACTNN_GREEDY_SAMPLE(T) \
+  greedy_sample_kernel<T><<<1, T, 0, s>>>(C, n, initial_bits, target, coef, b_out, word_offsets, wpb)
+    if (n <= 32) ACTNN_GREEDY_SAMPLE(32);
+    else if (n <= 64) ACTNN_GREEDY_SAMPLE(64);
+    else if (n <= 128) ACTNN_GREEDY_SAMPLE(128);
+    else if (n <= 256) ACTNN_GREEDY_SAMPLE(256);
+    else if (n <= 512) ACTNN_GREEDY_SAMPLE(512);
+    else ACTNN_GREEDY_SAMPLE(1024);
+#undef ACTNN_GREEDY_SAMPLE
+    return check_launch();
+  }
   if (w) greedy_kernel<true><<<1, kGreedyThreads, 0, s>>>(C, w, N, initial_bits, target, coef, b_out, word_offsets, wpb);
-  else if (candidates <= 256 * 8)
-    greedy_small_kernel<256, 8><<<1, 256, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
-  else if (candidates <= 512 * 8)
-    greedy_small_kernel<512, 8><<<1, 512, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
-  else if (candidates <= 1024 * 8)
-    greedy_small_kernel<1024, 8><<<1, 1024, 0, s>>>(C, N, initial_bits, target, coef, b_out, word_offsets, wpb);
   else greedy_kernel<false><<<1, kGreedyThreads, 0, s>>>(C, w, N, initial_bits, target, coef, b_out, word_offsets, wpb);
   return check_launch();
 }
