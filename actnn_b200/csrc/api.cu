@@ -1,4 +1,6 @@
 // Status strings, cached device properties, launch checking and the noise export.
+#include <mutex>
+
 #include "quant_math.cuh"
 
 namespace actnn {
@@ -20,7 +22,44 @@ const DeviceInfo& device_info() {
   return info[dev];
 }
 
-int check_launch() { return cudaPeekAtLastError() == cudaSuccess ? ACTNN_OK : ACTNN_ERR_LAUNCH; }
+// Kernels that stage inputs with bulk copies bound every wait on an mbarrier; a wait that
+// runs out adds one here and the warp stops.  Zero in every healthy run.
+__device__ unsigned g_bulk_wait_gave_up;
+
+unsigned* bulk_wait_counter() {
+  static unsigned* addr[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_bulk_wait_gave_up) == cudaSuccess) addr[dev] = (unsigned*)p;
+  }
+  return addr[dev];
+}
+
+// cudaGetLastError also clears a launch error, so one refused launch does not fail every later call.
+int check_launch() { return cudaGetLastError() == cudaSuccess ? ACTNN_OK : ACTNN_ERR_LAUNCH; }
+
+// Resident blocks per SM of a kernel (by entry address) on the current device, asked of the
+// occupancy calculator once and kept.  A first use with dynamic shared memory also raises
+// the kernel's limit to that size.
+int cached_blocks_per_sm(const void* kernel, int threads, int dynamic_smem) {
+  struct Entry { const void* fn; int dev; int n; };
+  static Entry table[512];
+  static int used = 0;
+  static std::mutex lock;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> guard(lock);
+  for (int i = 0; i < used; ++i)
+    if (table[i].fn == kernel && table[i].dev == dev) return table[i].n;
+  int n = 0;
+  if (dynamic_smem > 0) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dynamic_smem);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, dynamic_smem) != cudaSuccess || n <= 0) n = 1;
+  if (used < 512) table[used++] = Entry{kernel, dev, n};
+  return n;
+}
 
 namespace {
 
@@ -58,7 +97,14 @@ extern "C" const char* actnn_status_string(int status) {
   }
 }
 
-extern "C" int actnn_abi_version(void) { return 2; }
+extern "C" int actnn_abi_version(void) { return 3; }
+
+extern "C" int actnn_bulk_wait_failures(uint32_t* count) {
+  if (!count) return ACTNN_ERR_NULL;
+  unsigned* p = bulk_wait_counter();
+  if (!p) return ACTNN_ERR_LAUNCH;
+  return cudaMemcpy(count, p, sizeof(unsigned), cudaMemcpyDeviceToHost) == cudaSuccess ? ACTNN_OK : ACTNN_ERR_LAUNCH;
+}
 
 extern "C" int actnn_noise_fill(void* noise, int64_t numel, int dtype, uint64_t seed, uint64_t offset,
                                 actnn_stream_t stream) {

@@ -9,6 +9,8 @@
 // wpt samples' codes into eight bytes that it stores with one 8-byte store (256 B per
 // warp, contiguous).  The fused variant gets each group's min / max from two
 // redux.sync.f32 instructions on the same registers, so the activation is read once.
+#include <cstdlib>
+
 #include "quant_math.cuh"
 
 namespace actnn {
@@ -80,15 +82,23 @@ template <typename T, int BITS> struct TaskShape {
   static constexpr int ROUNDS = WPT / SS;
 };
 
-template <typename T, typename ST, int BITS, bool FUSED, bool FULL>
+// STAGED (whole tasks only): a round's OCTS octets per lane are SS contiguous runs of GP
+// groups in global memory.  Lane 0 asks the bulk-copy engine for the NEXT round's runs
+// while the warp works on the current one, into the warp's own two-stage ring in shared
+// memory, and every lane then reads its 16 / 32 bytes per octet from there; completion is
+// counted in bytes on one mbarrier per stage.  No register waits on DRAM, so the integer
+// pipe stays fed.
+constexpr int kStages = 2;
+template <typename T, typename ST, int BITS, bool FUSED, bool FULL, bool STAGED>
 __global__ void __launch_bounds__(kThreads, MagicInfo<T>::paired ? 3 : 2)
 pack_single_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T* __restrict__ mx,
                    int8_t* __restrict__ packed, ST* __restrict__ scale, ST* __restrict__ mn_out,
                    ST* __restrict__ mx_out, int64_t N, int64_t G, const T* __restrict__ noise,
-                   int stochastic, const NoiseKey key, int64_t total_bytes) {
+                   int stochastic, const NoiseKey key, int64_t total_bytes, unsigned* __restrict__ gave_up) {
   using Sh = TaskShape<T, BITS>;
   constexpr int WPT = Sh::WPT, OCTS = Sh::OCTS, SS = Sh::SS, GP = Sh::GP, ROUNDS = Sh::ROUNDS;
   static_assert(GP % NoiseShape<T>::GPC == 0, "a task covers whole Philox calls");
+  static_assert(!STAGED || FULL, "staging copies whole tasks");
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
@@ -99,6 +109,39 @@ pack_single_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T
   // the octet this lane prepares statistics for
   const int my_s = lane / GP, my_gi = lane % GP;
 
+  // ---- staging ring of this warp
+  extern __shared__ __align__(128) unsigned char staging[];
+  constexpr uint32_t kRoundBytes = OCTS * kGroup * sizeof(T);
+  constexpr uint32_t kRunBytes = GP * kGroup * sizeof(T);
+  uint32_t ring = 0, bars = 0, round_no = 0;
+  PairWalker ahead(warp, nwarps, nblocks, gblocks);
+  int ahead_rd = 0;
+  auto request = [&](uint32_t stage) {                         // lane 0: the round `ahead` points at
+    const int64_t a_n0 = ahead.no * WPT + ahead_rd * SS, a_g0 = (int64_t)ahead.r * GP;
+    const uint32_t bar = bars + 8u * stage, dst = ring + stage * kRoundBytes;
+    mbar_expect_tx(bar, kRoundBytes);
+#pragma unroll
+    for (int s = 0; s < SS; ++s) bulk_load(dst + s * kRunBytes, data + ((a_n0 + s) * G + a_g0) * kGroup, kRunBytes, bar);
+  };
+  auto advance = [&]() {
+    if (++ahead_rd == ROUNDS) { ahead_rd = 0; ahead.next(); }
+  };
+  if constexpr (STAGED) {
+    const uint32_t wib = threadIdx.x >> 5;
+    ring = smem_addr(staging) + wib * kStages * kRoundBytes;
+    bars = smem_addr(staging) + (kThreads / 32) * kStages * kRoundBytes + wib * kStages * 8u;
+    if (lane == 0) {
+#pragma unroll
+      for (int st = 0; st < kStages; ++st) mbar_init(bars + 8u * st, 1u);
+      mbar_init_fence();
+    }
+    __syncwarp();
+    if (ahead.valid()) {
+      if (lane == 0) request(0u);
+      advance();
+    }
+  }
+
   for (PairWalker walk(warp, nwarps, nblocks, gblocks); walk.valid(); walk.next()) {
     const int64_t no = walk.no;
     const int64_t g0 = (int64_t)walk.r * GP;
@@ -108,12 +151,33 @@ pack_single_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T
 #pragma unroll
     for (int rd = 0; rd < ROUNDS; ++rd) {
       const int64_t n0 = no * WPT + rd * SS;
-      Oct<T> x[OCTS];
+      Oct<T> x[STAGED ? 1 : OCTS] = {};                 // staged rounds are read from shared memory where used
+      uint32_t stage_base = 0;
+      auto octet = [&](int o) -> Oct<T> {
+        if constexpr (STAGED) return lds_oct<T>(stage_base + (uint32_t)(o * kGroup * sizeof(T)));
+        else return x[o];
+      };
+      if constexpr (STAGED) {
+        const uint32_t stage = round_no & 1u, parity = (round_no >> 1) & 1u;
+        __syncwarp();                                   // every lane has read the other stage
+        if (ahead.valid()) {
+          if (lane == 0) request(stage ^ 1u);
+          advance();
+        }
+        if (!__all_sync(kFull, mbar_wait(bars + 8u * stage, parity))) {
+          mbar_wait(bars + 8u * stage, parity);         // one more bounded wait for the copy in flight
+          if (lane == 0) atomicAdd(gave_up, 1u);
+          return;
+        }
+        stage_base = ring + stage * kRoundBytes + (uint32_t)(lane * kOct * sizeof(T));
+        ++round_no;
+      } else {
 #pragma unroll
-      for (int o = 0; o < OCTS; ++o) {
-        const int s = o / GP, gi = o % GP;
-        const bool ok = FULL || (n0 + s < N && gi < cnt);
-        x[o] = ok ? load_oct<T>(data + ((n0 + s) * G + g0 + gi) * kGroup + lane * kOct) : zero_oct<T>();
+        for (int o = 0; o < OCTS; ++o) {
+          const int s = o / GP, gi = o % GP;
+          const bool ok = FULL || (n0 + s < N && gi < cnt);
+          x[o] = ok ? load_oct<T>(data + ((n0 + s) * G + g0 + gi) * kGroup + lane * kOct) : zero_oct<T>();
+        }
       }
       // ---- statistics of the OCTS groups, one per lane
       float gmn = 0.f, gmx = 0.f;
@@ -123,7 +187,7 @@ pack_single_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T
 #pragma unroll
         for (int o = 0; o < OCTS; ++o) {
           float lo, hi;
-          oct_minmax<T>(x[o], lo, hi);
+          oct_minmax<T>(octet(o), lo, hi);
           lo = warp_min(lo);
           hi = warp_max(hi);
           if (lane == o) { gmn = lo; gmx = hi; }
@@ -157,7 +221,7 @@ pack_single_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T
           nz = nzb[gi % NoiseShape<T>::GPC];
         }
         // with the true minimum in hand the low clamp is implied by the rounding
-        const Magic<T> m = quantize_oct<T, !FUSED, BITS>(x[o], nz, qp);
+        const Magic<T> m = quantize_oct<T, !FUSED, BITS>(octet(o), nz, qp);
 #define ACTNN_ADD(K)                                                               \
         if constexpr (K < WPT) {                                                   \
           if (rd * SS + s == K) {                                                  \
@@ -283,22 +347,39 @@ int launch_pack(int bits, const void* data, const void* mn, const void* mx, int8
                 uint64_t seed, uint64_t offset, cudaStream_t s) {
   const NoiseKey key = make_noise_key(seed, offset);
   const int64_t tb = single_total_bytes(bits, N, G);
+  unsigned* gave_up = bulk_wait_counter();
+  // The staged variant is opt-in (environment ACTNN_STAGED_PACK=1): measured on a B200 it
+  // removes the waits on DRAM but not the kernel's real limit, instruction issue, and its
+  // start-up (every warp waits for its first round) costs more than that gains on tensors
+  // of ~100 MB.  Bulk copies want 16-byte aligned runs and whole tasks.
+  static const bool staged_wanted = [] {
+    const char* v = getenv("ACTNN_STAGED_PACK");
+    return v && v[0] == '1';
+  }();
+  const bool can_stage = staged_wanted && gave_up != nullptr && aligned(data, 16);
 #define ACTNN_LAUNCH(BITS)                                                                          \
   {                                                                                                 \
     using Sh = TaskShape<T, BITS>;                                                                  \
+    constexpr int smem = (kThreads / 32) * (kStages * Sh::OCTS * kGroup * (int)sizeof(T) + kStages * 8); \
     const int64_t tasks = ((N + Sh::WPT - 1) / Sh::WPT) * ((G + Sh::GP - 1) / Sh::GP);              \
-    /* whole tasks only, each starting on a Philox call boundary */                                \
     const bool full = N % Sh::WPT == 0 && G % Sh::GP == 0;                                          \
-    const int grid = full ? persistent_grid(pack_single_kernel<T, ST, BITS, FUSED, true>, kThreads, tasks)   \
-                          : persistent_grid(pack_single_kernel<T, ST, BITS, FUSED, false>, kThreads, tasks); \
-    if (full)                                                                                       \
-      pack_single_kernel<T, ST, BITS, FUSED, true><<<grid, kThreads, 0, s>>>(                       \
+    if (full && can_stage) {                                                                        \
+      auto kernel = pack_single_kernel<T, ST, BITS, FUSED, true, true>;                             \
+      const int grid = persistent_grid(kernel, kThreads, tasks, smem);                              \
+      kernel<<<grid, kThreads, smem, s>>>((const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, \
+                                          (ST*)mn_out, (ST*)mx_out, N, G, (const T*)noise, stochastic, key, tb, \
+                                          gave_up);                                                 \
+    } else if (full) {                                                                              \
+      auto kernel = pack_single_kernel<T, ST, BITS, FUSED, true, false>;                            \
+      kernel<<<persistent_grid(kernel, kThreads, tasks), kThreads, 0, s>>>(                         \
           (const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, (ST*)mn_out, (ST*)mx_out, N, G, \
-          (const T*)noise, stochastic, key, tb);                                                    \
-    else                                                                                            \
-      pack_single_kernel<T, ST, BITS, FUSED, false><<<grid, kThreads, 0, s>>>(                      \
+          (const T*)noise, stochastic, key, tb, gave_up);                                           \
+    } else {                                                                                        \
+      auto kernel = pack_single_kernel<T, ST, BITS, FUSED, false, false>;                           \
+      kernel<<<persistent_grid(kernel, kThreads, tasks), kThreads, 0, s>>>(                         \
           (const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, (ST*)mn_out, (ST*)mx_out, N, G, \
-          (const T*)noise, stochastic, key, tb);                                                    \
+          (const T*)noise, stochastic, key, tb, gave_up);                                           \
+    }                                                                                               \
   }
   switch (bits) {
     case 1: ACTNN_LAUNCH(1); break;

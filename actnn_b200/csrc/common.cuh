@@ -71,6 +71,58 @@ template <> ACTNN_DEV Oct<float> zero_oct<float>() {
   return o;
 }
 
+// ------------------------------------------------------------------ bulk copies into shared memory
+// A warp stages its next inputs with the bulk-copy engine (cp.async.bulk, completion counted
+// in bytes on an mbarrier) so that no register waits on DRAM.  Addresses are 32-bit shared
+// window addresses; source, destination and size must be multiples of 16 bytes.
+ACTNN_DEV uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+ACTNN_DEV void mbar_init(uint32_t bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(arrivals) : "memory");
+}
+ACTNN_DEV void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+ACTNN_DEV void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+ACTNN_DEV void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// One attempt may sleep in hardware for up to about kBulkWaitHintNs before it reports failure.
+constexpr uint32_t kBulkWaitHintNs = 20000u;
+ACTNN_DEV bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity), "r"(kBulkWaitHintNs) : "memory");
+  return ok != 0;
+}
+// Waits for the phase with the given parity, at most kBulkWaitTries attempts (each attempt
+// itself sleeps in hardware for a bounded time).  false = gave up.
+constexpr uint32_t kBulkWaitTries = 1u << 16;
+ACTNN_DEV bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kBulkWaitTries; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+template <typename T> ACTNN_DEV Oct<T> lds_oct(uint32_t addr) {
+  Oct<T> o;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(o.r[0]), "=r"(o.r[1]), "=r"(o.r[2]), "=r"(o.r[3]) : "r"(addr));
+  return o;
+}
+template <> ACTNN_DEV Oct<float> lds_oct<float>(uint32_t addr) {
+  Oct<float> o;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(o.f[0]), "=f"(o.f[1]), "=f"(o.f[2]), "=f"(o.f[3]) : "r"(addr));
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(o.f[4]), "=f"(o.f[5]), "=f"(o.f[6]), "=f"(o.f[7]) : "r"(addr + 16u));
+  return o;
+}
+
 // ------------------------------------------------------------------ warp reductions
 ACTNN_DEV float warp_min(float v) {
   float r;
@@ -174,6 +226,7 @@ ACTNN_DEV Philox4 noise_call(const NoiseKey& key, uint64_t c) {
 struct DeviceInfo { int sm_count; };
 const DeviceInfo& device_info();                   // api.cu (per current device, cached)
 int check_launch();                                // api.cu: cudaPeekAtLastError -> status
+unsigned* bulk_wait_counter();                     // api.cu: device counter of bulk-copy waits that gave up
 
 static inline bool aligned(const void* p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 
@@ -181,18 +234,13 @@ static inline bool aligned(const void* p, size_t a) { return ((uintptr_t)p & (a 
 // Grid for a persistent warp-task kernel: as many blocks as can be resident at once
 // (SMs x blocks per SM), so that there is a single wave and no under-filled tail, but no
 // more than the tasks need.  The occupancy query is cached per kernel and device.
+// `dynamic_smem` > 0 also raises the kernel's dynamic shared memory limit to that size.
+int cached_blocks_per_sm(const void* kernel, int threads, int dynamic_smem);   // api.cu
+
 template <typename Kernel>
-int persistent_grid(Kernel kernel, int threads, int64_t warp_tasks) {
-  static int per_sm[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (per_sm[dev] == 0) {
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n <= 0) n = 1;
-    per_sm[dev] = n;
-  }
-  const int64_t resident = (int64_t)device_info().sm_count * per_sm[dev];
+int persistent_grid(Kernel kernel, int threads, int64_t warp_tasks, int dynamic_smem = 0) {
+  const int per_sm = cached_blocks_per_sm((const void*)kernel, threads, dynamic_smem);
+  const int64_t resident = (int64_t)device_info().sm_count * per_sm;
   const int64_t needed = (warp_tasks + threads / 32 - 1) / (threads / 32);
   const int64_t grid = needed < resident ? needed : resident;
   return (int)(grid < 1 ? 1 : grid);

@@ -282,6 +282,14 @@ int actnn_batch_norm_backward(const void* x, const void* grad_out, const float* 
                               actnn_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * How many bulk-copy waits gave up on the current device since the library was loaded.
+ * The opt-in staged pack kernels (environment ACTNN_STAGED_PACK=1) copy their inputs into
+ * shared memory with the bulk-copy engine and bound every wait on the completion barrier;
+ * a warp whose wait runs out stops and leaves its outputs unwritten.  Zero in every
+ * healthy run; reading it synchronises with the device.  No counterpart in the reference. */
+int actnn_bulk_wait_failures(uint32_t* count);
+
+/* ------------------------------------------------------------------------------------
  * The rounding noise the pack kernels draw for (seed, offset) when `noise == NULL`,
  * written as a [numel] array of `dtype` indexed like the padded [N, G, 256] activation.
  * No counterpart in the reference (it draws cuRAND numbers it cannot replay); exists so

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import actnn_oracle as O
-from conftest import DTYPES, from_raw, load_cases, same_values
+from conftest import DTYPES, ROOT, from_raw, load_cases, same_values
 
 pytestmark = pytest.mark.gpu
 
@@ -391,3 +391,40 @@ def test_sample_sumsq(ext, dtype, shape):
     assert got.dtype == torch.float32 and torch.allclose(got.cpu(), ref, rtol=1e-3)
     sliced = dev(g)[1:]                                       # a view that does not start the allocation
     assert torch.allclose(ext.cp.sample_sumsq(sliced).cpu(), ref[1:], rtol=1e-3)
+
+
+def test_staged_pack_matches_direct_pack():
+    """The opt-in bulk-copy staged pack (ACTNN_STAGED_PACK=1, read when the library first
+    packs) against the default kernel, in a child process; its wait counter must stay zero."""
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import ctypes, sys, torch
+sys.path.insert(0, %r)
+from actnn_b200 import _lib
+from actnn_b200.cpp_extension import quantization as q
+g = torch.Generator().manual_seed(5)
+x = torch.relu(torch.randn(16, 12, 256, generator=g)).to(torch.float16).cuda()
+out = []
+for dtype in (torch.float16, torch.bfloat16, torch.float32):
+    for bits in (1, 2, 4, 8):
+        p, s, m = q.compress_single_precision(x.to(dtype), bits, True, philox=(7, 0))
+        out.append(p.cpu())
+torch.cuda.synchronize()
+count = ctypes.c_uint32(123)
+_lib.check(_lib.load().actnn_bulk_wait_failures(ctypes.byref(count)), "actnn_bulk_wait_failures")
+assert count.value == 0, count.value
+torch.save(out, sys.argv[1])
+""" % ROOT
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        results = []
+        for flag in ("0", "1"):
+            path = os.path.join(tmp, "out%s.pt" % flag)
+            env = dict(os.environ, ACTNN_STAGED_PACK=flag)
+            subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=300)
+            results.append(torch.load(path))
+    assert len(results[0]) == 12
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
