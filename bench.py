@@ -456,7 +456,7 @@ def resnet_throughput(level: str, batch: int, steps: int, warmup: int, dev, worl
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         before = torch.cuda.memory_allocated(dev)
-        with torch.autocast("cuda", dtype=dt):
+        with torch.autocast("cuda", dtype=dt, enabled=dt != torch.float32):
             out = model(images)
             loss = crit(out, target)
         if it == warmup - 1:
@@ -499,6 +499,10 @@ def run_resnet(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             res[level]["ms_per_step"] = float(t.item())
             res[level]["images_per_s_per_gpu"] = round(args.batch / float(t.item()) * 1e3, 1)
+    # the reference's memory tables compare with float32 training: one float32 exact step for its bytes
+    fp32_act = None
+    if world == 1 and args.amp != "float32":
+        fp32_act = resnet_throughput("exact", args.batch, 1, 1, dev, world, args.arch, "float32")["activation_bytes"]
     if rank == 0:
         q, e = res[args.level], res["exact"]
         print(json.dumps({
@@ -512,6 +516,8 @@ def run_resnet(args):
             "ratio_to_exact": round(q["images_per_s_per_gpu"] / e["images_per_s_per_gpu"], 4),
             "activation_bytes": q["activation_bytes"], "exact_activation_bytes": e["activation_bytes"],
             "activation_reduction_vs_%s_autocast" % args.amp: round(e["activation_bytes"] / max(q["activation_bytes"], 1), 2),
+            "exact_float32_activation_bytes": fp32_act,
+            "activation_reduction_vs_float32": None if not fp32_act else round(fp32_act / max(q["activation_bytes"], 1), 2),
         }))
     if world > 1:
         dist.destroy_process_group()
