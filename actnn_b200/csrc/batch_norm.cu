@@ -25,6 +25,7 @@ namespace {
 
 constexpr int kBnThreads = 256;
 constexpr int kBnUnroll = 4;
+constexpr int kBnReduceUnroll = 8;     // the forward reduce has one input stream: twice the loads in flight
 
 // n / d for n < 2^31 by multiply-high: q = (umulhi(n, m) + n) >> s.
 struct FastDiv {
@@ -133,10 +134,10 @@ bn_forward_reduce_kernel(const T* __restrict__ x, BnShape sh, float2* __restrict
   const float shift = to_float<T>(x[(int64_t)c * sh.HW]);
   const T* base = x + ((int64_t)n0 * sh.C + c) * sh.HW;
   float sum = 0.f, sq = 0.f;
-  for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kBnThreads * kBnUnroll) {
-    Vec<T, VEC> v[kBnUnroll];
+  for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kBnThreads * kBnReduceUnroll) {
+    Vec<T, VEC> v[kBnReduceUnroll];
 #pragma unroll
-    for (int u = 0; u < kBnUnroll; ++u) {
+    for (int u = 0; u < kBnReduceUnroll; ++u) {
       const uint32_t idx = i0 + u * kBnThreads;
       if (idx < total) {
         const uint32_t n = fdiv(idx, sh.vecs_per_plane), off = idx - n * vpp;
@@ -144,7 +145,7 @@ bn_forward_reduce_kernel(const T* __restrict__ x, BnShape sh, float2* __restrict
       }
     }
 #pragma unroll
-    for (int u = 0; u < kBnUnroll; ++u) {
+    for (int u = 0; u < kBnReduceUnroll; ++u) {
       if (i0 + u * kBnThreads < total) {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
@@ -282,9 +283,18 @@ bn_backward_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* _
 }
 
 // ------------------------------------------------------------------ host side
+// Upper bound of the splits per channel (sizes the workspace): about 8 blocks per SM.
 int splits_for(int64_t N, int64_t C) {
   const int64_t want = ((int64_t)device_info().sm_count * 8 + C - 1) / C;
   int64_t S = max((int64_t)1, min(min(N, want), (int64_t)65535));
+  const int64_t pps = (N + S - 1) / S;
+  return (int)((N + pps - 1) / pps);
+}
+// Splits for one reduce kernel: C * S blocks should fill the blocks that kernel can keep
+// resident but not spill into a second, mostly empty wave.
+int splits_for_kernel(const void* kernel, int64_t N, int64_t C, int cap) {
+  const int64_t resident = (int64_t)device_info().sm_count * cached_blocks_per_sm(kernel, kBnThreads, 0);
+  int64_t S = max((int64_t)1, min((int64_t)cap, resident / max(C, (int64_t)1)));
   const int64_t pps = (N + S - 1) / S;
   return (int)((N + pps - 1) / pps);
 }
@@ -331,7 +341,8 @@ int apply_grid(int64_t total_vecs) {
 template <typename T, int VEC>
 int forward_vec(const T* x, const float* weight, const float* bias, float* running_mean, float* running_var, T* y,
                 float* save_mean, float* save_invstd, int64_t N, int64_t C, int64_t HW, float momentum, float eps,
-                Workspace w, int S, cudaStream_t s) {
+                Workspace w, int cap, cudaStream_t s) {
+  const int S = splits_for_kernel((const void*)bn_forward_reduce_kernel<T, VEC>, N, C, cap);
   BnShape sh{(int)N, (int)C, (int)HW, S, (int)((N + S - 1) / S), make_fastdiv((uint32_t)(HW / VEC))};
   bn_forward_reduce_kernel<T, VEC><<<dim3((unsigned)C, (unsigned)S), kBnThreads, 0, s>>>(
       x, sh, w.partial, w.tickets, weight, bias, running_mean, running_var, save_mean, save_invstd, w.coef,
@@ -362,8 +373,9 @@ int forward_typed(const void* x, const float* weight, const float* bias, float* 
 
 template <typename T, int VEC>
 int backward_vec(const T* x, const T* dy, const float* weight, const float* save_mean, const float* save_invstd,
-                 T* dx, float* dweight, float* dbias, int64_t N, int64_t C, int64_t HW, Workspace w, int S,
+                 T* dx, float* dweight, float* dbias, int64_t N, int64_t C, int64_t HW, Workspace w, int cap,
                  cudaStream_t s) {
+  const int S = splits_for_kernel((const void*)bn_backward_reduce_kernel<T, VEC>, N, C, cap);
   BnShape sh{(int)N, (int)C, (int)HW, S, (int)((N + S - 1) / S), make_fastdiv((uint32_t)(HW / VEC))};
   bn_backward_reduce_kernel<T, VEC><<<dim3((unsigned)C, (unsigned)S), kBnThreads, 0, s>>>(
       x, dy, sh, w.partial, w.tickets, weight, save_mean, save_invstd, dweight, dbias, w.coef);

@@ -575,6 +575,23 @@ def run_profile(args):
         "relu_backward": lambda: lib.actnn_relu_backward(x.data_ptr(), mask.data_ptr(), out.data_ptr(), x.numel(),
                                                         F16, st),
     }
+    # batch norm over the same bytes viewed as NCHW [512, 256, 28, 28]
+    bn_c, bn_hw = 256, 784
+    w = torch.ones(bn_c, device=dev)
+    bvec = torch.zeros(bn_c, device=dev)
+    rm, rv = torch.zeros(bn_c, device=dev), torch.ones(bn_c, device=dev)
+    sm, si = torch.empty(bn_c, device=dev), torch.empty(bn_c, device=dev)
+    gw, gb = torch.empty(bn_c, device=dev), torch.empty(bn_c, device=dev)
+    dy = torch.randn_like(x)
+    ws_bytes = lib.actnn_batch_norm_workspace(N, bn_c, bn_hw)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    calls["batch_norm_forward"] = lambda: lib.actnn_batch_norm_forward(
+        x.data_ptr(), w.data_ptr(), bvec.data_ptr(), rm.data_ptr(), rv.data_ptr(), out.data_ptr(), sm.data_ptr(),
+        si.data_ptr(), N, bn_c, bn_hw, 0.1, 1e-5, F16, ws.data_ptr(), ws_bytes, st)
+    calls["batch_norm_backward"] = lambda: lib.actnn_batch_norm_backward(
+        x.data_ptr(), dy.data_ptr(), w.data_ptr(), sm.data_ptr(), si.data_ptr(), out.data_ptr(), gw.data_ptr(),
+        gb.data_ptr(), N, bn_c, bn_hw, F16, ws.data_ptr(), ws_bytes, st)
+    calls["batch_norm_forward"]()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     names = list(calls) if args.profile == "all" else [args.profile]
