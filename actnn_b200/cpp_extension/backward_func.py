@@ -8,7 +8,10 @@ argument order and are routed to that operator: the dense convolution math stays
 ``cudnn_batch_norm`` / ``cudnn_batch_norm_backward`` keep the reference's names, arguments
 and return values, but the training-mode work is done by this package's own kernels
 (``actnn_batch_norm_forward`` / ``actnn_batch_norm_backward`` of the C ABI), which spread a
-channel over many blocks instead of cuDNN's one block per channel."""
+channel over many blocks instead of cuDNN's one block per channel.  ``batch_norm_stats``,
+``batch_norm_elemt``, ``batch_norm_backward_reduce`` and ``batch_norm_backward_elemt`` are
+the same kernels under the names of the ATen operators the reference's synchronised batch
+norm calls (ops.py:515-603)."""
 import torch
 
 from .. import _lib
@@ -109,6 +112,70 @@ def cudnn_batch_norm_backward(input, grad_output, weight, running_mean, running_
     if weight is not None and weight.dtype != torch.float32:
         dweight, dbias = dweight.to(weight.dtype), dbias.to(weight.dtype)
     return dx, dweight, dbias
+
+
+def batch_norm_stats(input, eps):
+    """``torch.batch_norm_stats``: per-channel ``(mean, invstd)`` of this rank's batch
+    (reference call site: ops.py:515)."""
+    x = input.contiguous()
+    N, C, HW = _bn_dims(x)
+    mean = torch.empty(C, dtype=torch.float32, device=x.device)
+    invstd = torch.empty(C, dtype=torch.float32, device=x.device)
+    ws, nbytes = _bn_workspace(N, C, HW, x.device)
+    _lib.call("actnn_batch_norm_stats", x, _lib.ptr(x), _lib.ptr(mean), _lib.ptr(invstd), N, C, HW, float(eps),
+              _lib.dtype_id(x.dtype), _lib.ptr(ws), nbytes, _lib.stream_of(x))
+    return mean, invstd
+
+
+def batch_norm_elemt(input, weight, bias, mean, invstd, eps):
+    """``torch.batch_norm_elemt``: normalise with given statistics (ops.py:554)."""
+    x = input.contiguous()
+    N, C, HW = _bn_dims(x)
+    y = torch.empty_like(x)
+    ws = torch.empty(max(16 * C, 16), dtype=torch.uint8, device=x.device)
+    _lib.call("actnn_batch_norm_elemt", x, _lib.ptr(x), _lib.ptr(_as_f32(weight)), _lib.ptr(_as_f32(bias)),
+              _lib.ptr(_as_f32(mean)), _lib.ptr(_as_f32(invstd)), _lib.ptr(y), N, C, HW, _lib.dtype_id(x.dtype),
+              _lib.ptr(ws), 16 * C, _lib.stream_of(x))
+    return y
+
+
+def batch_norm_backward_reduce(grad_out, input, mean, invstd, weight, input_g, weight_g, bias_g):
+    """``torch.batch_norm_backward_reduce``: ``(sum_dy, sum_dy_xmu, grad_weight, grad_bias)`` of this
+    rank (ops.py:570-577)."""
+    x = input.contiguous()
+    dy = grad_out.contiguous()
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    N, C, HW = _bn_dims(x)
+    sum_dy = torch.empty(C, dtype=torch.float32, device=x.device)
+    sum_dy_xmu = torch.empty(C, dtype=torch.float32, device=x.device)
+    grad_weight = torch.empty(C, dtype=torch.float32, device=x.device)
+    ws, nbytes = _bn_workspace(N, C, HW, x.device)
+    _lib.call("actnn_batch_norm_backward_reduce", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(_as_f32(weight)),
+              _lib.ptr(_as_f32(mean)), _lib.ptr(_as_f32(invstd)), _lib.ptr(sum_dy), _lib.ptr(sum_dy_xmu),
+              _lib.ptr(grad_weight), N, C, HW, _lib.dtype_id(x.dtype), _lib.ptr(ws), nbytes, _lib.stream_of(x))
+    grad_bias = sum_dy
+    if weight is not None and weight.dtype != torch.float32:
+        grad_weight, grad_bias = grad_weight.to(weight.dtype), grad_bias.to(weight.dtype)
+    return sum_dy, sum_dy_xmu, (grad_weight if weight_g else None), (grad_bias if bias_g else None)
+
+
+def batch_norm_backward_elemt(grad_out, input, mean, invstd, weight, sum_dy, sum_dy_xmu, count):
+    """``torch.batch_norm_backward_elemt``: the input gradient from sums over all ranks; ``count``
+    holds every rank's elements per channel and stays on the device (ops.py:594-603)."""
+    x = input.contiguous()
+    dy = grad_out.contiguous()
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    N, C, HW = _bn_dims(x)
+    counts = count.reshape(-1).to(torch.float32).contiguous()
+    dx = torch.empty_like(x)
+    ws = torch.empty(max(16 * C, 16), dtype=torch.uint8, device=x.device)
+    _lib.call("actnn_batch_norm_backward_elemt", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(_as_f32(weight)),
+              _lib.ptr(_as_f32(mean)), _lib.ptr(_as_f32(invstd)), _lib.ptr(sum_dy.contiguous()),
+              _lib.ptr(sum_dy_xmu.contiguous()), _lib.ptr(counts), counts.numel(), _lib.ptr(dx), N, C, HW,
+              _lib.dtype_id(x.dtype), _lib.ptr(ws), 16 * C, _lib.stream_of(x))
+    return dx
 
 
 def native_batch_norm(input, weight, bias, running_mean, running_var, training, momentum, eps):

@@ -208,7 +208,7 @@ bn_backward_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, BnS
                           float2* __restrict__ partial, unsigned* __restrict__ tickets,
                           const float* __restrict__ weight, const float* __restrict__ save_mean,
                           const float* __restrict__ save_invstd, float* __restrict__ dweight,
-                          float* __restrict__ dbias, float4* __restrict__ coef) {
+                          float* __restrict__ dbias, float* __restrict__ sum_dy_xmu, float4* __restrict__ coef) {
   const int c = blockIdx.x, s = blockIdx.y;
   const int n0 = s * sh.planes_per_split, n1 = min(sh.N, n0 + sh.planes_per_split);
   const uint32_t vpp = sh.vecs_per_plane.d, total = (uint32_t)(n1 - n0) * vpp;
@@ -246,6 +246,7 @@ bn_backward_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, BnS
   const float invstd = save_invstd[c];
   if (dbias) dbias[c] = tot.x;
   if (dweight) dweight[c] = tot.y * invstd;
+  if (sum_dy_xmu) sum_dy_xmu[c] = tot.y;
   coef[c] = make_float4(mean, (weight ? weight[c] : 1.f) * invstd, tot.x / M, tot.y * invstd * invstd / M);
 }
 
@@ -279,6 +280,29 @@ bn_backward_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* _
         o.store(dx + (int64_t)idx * VEC);
       }
     }
+  }
+}
+
+// Coefficients of the apply passes from statistics that were combined elsewhere (across
+// ranks): the two halves of a synchronised batch norm.
+__global__ void bn_forward_coef_kernel(const float* __restrict__ mean, const float* __restrict__ invstd,
+                                       const float* __restrict__ weight, const float* __restrict__ bias,
+                                       float4* __restrict__ coef, int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < C) coef[c] = make_float4(mean[c], invstd[c] * (weight ? weight[c] : 1.f), bias ? bias[c] : 0.f, 0.f);
+}
+__global__ void bn_backward_coef_kernel(const float* __restrict__ mean, const float* __restrict__ invstd,
+                                        const float* __restrict__ weight, const float* __restrict__ sum_dy,
+                                        const float* __restrict__ sum_dy_xmu, const float* __restrict__ counts,
+                                        int n_counts, float4* __restrict__ coef, int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  float total = 0.f;                                           // elements per channel over all ranks
+  for (int i = 0; i < n_counts; ++i) total += counts[i];
+  const float inv_count = 1.f / total;
+  if (c < C) {
+    const float is = invstd[c];
+    coef[c] = make_float4(mean[c], (weight ? weight[c] : 1.f) * is, sum_dy[c] * inv_count,
+                          sum_dy_xmu[c] * is * is * inv_count);
   }
 }
 
@@ -348,6 +372,7 @@ int forward_vec(const T* x, const float* weight, const float* bias, float* runni
       x, sh, w.partial, w.tickets, weight, bias, running_mean, running_var, save_mean, save_invstd, w.coef,
       momentum, eps);
   if (int st = check_launch()) return st;
+  if (!y) return ACTNN_OK;
   const int64_t total_vecs = N * C * (HW / VEC);
   if (total_vecs >= ((int64_t)1 << 31)) return ACTNN_ERR_SHAPE;
   bn_forward_apply_kernel<T, VEC><<<apply_grid(total_vecs), kBnThreads, 0, s>>>(
@@ -373,12 +398,12 @@ int forward_typed(const void* x, const float* weight, const float* bias, float* 
 
 template <typename T, int VEC>
 int backward_vec(const T* x, const T* dy, const float* weight, const float* save_mean, const float* save_invstd,
-                 T* dx, float* dweight, float* dbias, int64_t N, int64_t C, int64_t HW, Workspace w, int cap,
-                 cudaStream_t s) {
+                 T* dx, float* dweight, float* dbias, float* sum_dy_xmu, int64_t N, int64_t C, int64_t HW,
+                 Workspace w, int cap, cudaStream_t s) {
   const int S = splits_for_kernel((const void*)bn_backward_reduce_kernel<T, VEC>, N, C, cap);
   BnShape sh{(int)N, (int)C, (int)HW, S, (int)((N + S - 1) / S), make_fastdiv((uint32_t)(HW / VEC))};
   bn_backward_reduce_kernel<T, VEC><<<dim3((unsigned)C, (unsigned)S), kBnThreads, 0, s>>>(
-      x, dy, sh, w.partial, w.tickets, weight, save_mean, save_invstd, dweight, dbias, w.coef);
+      x, dy, sh, w.partial, w.tickets, weight, save_mean, save_invstd, dweight, dbias, sum_dy_xmu, w.coef);
   if (int st = check_launch()) return st;
   if (!dx) return ACTNN_OK;
   const int64_t total_vecs = N * C * (HW / VEC);
@@ -390,11 +415,11 @@ int backward_vec(const T* x, const T* dy, const float* weight, const float* save
 
 template <typename T>
 int backward_typed(const void* x, const void* dy, const float* weight, const float* save_mean,
-                   const float* save_invstd, void* dx, float* dweight, float* dbias, int64_t N, int64_t C,
-                   int64_t HW, Workspace w, int S, cudaStream_t s) {
+                   const float* save_invstd, void* dx, float* dweight, float* dbias, float* sum_dy_xmu,
+                   int64_t N, int64_t C, int64_t HW, Workspace w, int S, cudaStream_t s) {
 #define ACTNN_BN_BWD(V)                                                                                      \
   return backward_vec<T, V>((const T*)x, (const T*)dy, weight, save_mean, save_invstd, (T*)dx, dweight, dbias, \
-                            N, C, HW, w, S, s)
+                            sum_dy_xmu, N, C, HW, w, S, s)
   switch (vec_width<T>(HW, x, dy, dx)) {
     case 8: if constexpr (sizeof(T) == 2) { ACTNN_BN_BWD(8); }
     case 4: ACTNN_BN_BWD(4);
@@ -402,6 +427,47 @@ int backward_typed(const void* x, const void* dy, const float* weight, const flo
     default: ACTNN_BN_BWD(1);
   }
 #undef ACTNN_BN_BWD
+}
+
+template <typename T>
+int forward_apply_typed(const void* x, void* y, const float4* coef, int64_t N, int64_t C, int64_t HW,
+                        cudaStream_t s) {
+  const int vec = vec_width<T>(HW, x, y, nullptr);
+  const int64_t total_vecs = N * C * (HW / vec);
+  if (total_vecs >= ((int64_t)1 << 31)) return ACTNN_ERR_SHAPE;
+  const FastDiv vpp = make_fastdiv((uint32_t)(HW / vec)), ch = make_fastdiv((uint32_t)C);
+  const int grid = apply_grid(total_vecs);
+#define ACTNN_BN_APPLY(V) \
+  bn_forward_apply_kernel<T, V><<<grid, kBnThreads, 0, s>>>((const T*)x, (T*)y, coef, (uint32_t)total_vecs, vpp, ch)
+  switch (vec) {
+    case 8: if constexpr (sizeof(T) == 2) { ACTNN_BN_APPLY(8); } break;
+    case 4: ACTNN_BN_APPLY(4); break;
+    case 2: ACTNN_BN_APPLY(2); break;
+    default: ACTNN_BN_APPLY(1); break;
+  }
+#undef ACTNN_BN_APPLY
+  return check_launch();
+}
+
+template <typename T>
+int backward_apply_typed(const void* x, const void* dy, void* dx, const float4* coef, int64_t N, int64_t C,
+                         int64_t HW, cudaStream_t s) {
+  const int vec = vec_width<T>(HW, x, dy, dx);
+  const int64_t total_vecs = N * C * (HW / vec);
+  if (total_vecs >= ((int64_t)1 << 31)) return ACTNN_ERR_SHAPE;
+  const FastDiv vpp = make_fastdiv((uint32_t)(HW / vec)), ch = make_fastdiv((uint32_t)C);
+  const int grid = apply_grid(total_vecs);
+#define ACTNN_BN_APPLY(V)                                                                                  \
+  bn_backward_apply_kernel<T, V><<<grid, kBnThreads, 0, s>>>((const T*)x, (const T*)dy, (T*)dx, coef,        \
+                                                            (uint32_t)total_vecs, vpp, ch)
+  switch (vec) {
+    case 8: if constexpr (sizeof(T) == 2) { ACTNN_BN_APPLY(8); } break;
+    case 4: ACTNN_BN_APPLY(4); break;
+    case 2: ACTNN_BN_APPLY(2); break;
+    default: ACTNN_BN_APPLY(1); break;
+  }
+#undef ACTNN_BN_APPLY
+  return check_launch();
 }
 
 }  // namespace
@@ -421,7 +487,7 @@ extern "C" int actnn_batch_norm_forward(const void* x, const float* weight, cons
   if (int st = check_shape(N, C, HW)) return st;
   if (C == 0) return ACTNN_OK;
   if (N * HW == 0) return ACTNN_ERR_SHAPE;                     // statistics of an empty batch
-  if (!x || !y || !save_mean || !save_invstd || !workspace) return ACTNN_ERR_NULL;
+  if (!x || !save_mean || !save_invstd || !workspace) return ACTNN_ERR_NULL;   // y NULL: statistics only
   const int S = splits_for(N, C);
   if (workspace_bytes < workspace_bytes_for(C, S) || !aligned(workspace, 16)) return ACTNN_ERR_CAPACITY;
   cudaStream_t s = (cudaStream_t)stream;
@@ -457,14 +523,93 @@ extern "C" int actnn_batch_norm_backward(const void* x, const void* grad_out, co
   if (cudaMemsetAsync(w.tickets, 0, 4 * C, s) != cudaSuccess) return ACTNN_ERR_LAUNCH;
   switch (dtype) {
     case ACTNN_F32:
-      return backward_typed<float>(x, grad_out, weight, save_mean, save_invstd, grad_in, grad_weight, grad_bias, N,
-                                   C, HW, w, S, s);
+      return backward_typed<float>(x, grad_out, weight, save_mean, save_invstd, grad_in, grad_weight, grad_bias,
+                                   nullptr, N, C, HW, w, S, s);
     case ACTNN_F16:
       return backward_typed<__half>(x, grad_out, weight, save_mean, save_invstd, grad_in, grad_weight, grad_bias,
-                                    N, C, HW, w, S, s);
+                                    nullptr, N, C, HW, w, S, s);
     case ACTNN_BF16:
       return backward_typed<__nv_bfloat16>(x, grad_out, weight, save_mean, save_invstd, grad_in, grad_weight,
-                                           grad_bias, N, C, HW, w, S, s);
+                                           grad_bias, nullptr, N, C, HW, w, S, s);
+    default: return ACTNN_ERR_DTYPE;
+  }
+}
+
+// ---- the four halves a synchronised batch norm is made of (statistics are combined across
+// ranks between them)
+extern "C" int actnn_batch_norm_stats(const void* x, float* mean, float* invstd, int64_t N, int64_t C, int64_t HW,
+                                      double eps, int dtype, void* workspace, int64_t workspace_bytes,
+                                      actnn_stream_t stream) {
+  return actnn_batch_norm_forward(x, nullptr, nullptr, nullptr, nullptr, nullptr, mean, invstd, N, C, HW, 0.0, eps,
+                                  dtype, workspace, workspace_bytes, stream);
+}
+
+extern "C" int actnn_batch_norm_elemt(const void* x, const float* weight, const float* bias, const float* mean,
+                                      const float* invstd, void* y, int64_t N, int64_t C, int64_t HW, int dtype,
+                                      void* workspace, int64_t workspace_bytes, actnn_stream_t stream) {
+  if (int st = check_shape(N, C, HW)) return st;
+  if (N * C * HW == 0) return ACTNN_OK;
+  if (!x || !y || !mean || !invstd || !workspace) return ACTNN_ERR_NULL;
+  if (workspace_bytes < 16 * C || !aligned(workspace, 16)) return ACTNN_ERR_CAPACITY;
+  cudaStream_t s = (cudaStream_t)stream;
+  float4* coef = (float4*)workspace;
+  bn_forward_coef_kernel<<<(unsigned)((C + 255) / 256), 256, 0, s>>>(mean, invstd, weight, bias, coef, (int)C);
+  switch (dtype) {
+    case ACTNN_F32: return forward_apply_typed<float>(x, y, coef, N, C, HW, s);
+    case ACTNN_F16: return forward_apply_typed<__half>(x, y, coef, N, C, HW, s);
+    case ACTNN_BF16: return forward_apply_typed<__nv_bfloat16>(x, y, coef, N, C, HW, s);
+    default: return ACTNN_ERR_DTYPE;
+  }
+}
+
+extern "C" int actnn_batch_norm_backward_reduce(const void* x, const void* grad_out, const float* weight,
+                                                const float* mean, const float* invstd, float* sum_dy,
+                                                float* sum_dy_xmu, float* grad_weight, int64_t N, int64_t C,
+                                                int64_t HW, int dtype, void* workspace, int64_t workspace_bytes,
+                                                actnn_stream_t stream) {
+  if (int st = check_shape(N, C, HW)) return st;
+  if (C == 0) return ACTNN_OK;
+  if (N * HW == 0) return ACTNN_ERR_SHAPE;
+  if (!x || !grad_out || !mean || !invstd || !workspace) return ACTNN_ERR_NULL;
+  const int S = splits_for(N, C);
+  if (workspace_bytes < workspace_bytes_for(C, S) || !aligned(workspace, 16)) return ACTNN_ERR_CAPACITY;
+  cudaStream_t s = (cudaStream_t)stream;
+  Workspace w = carve(workspace, C, S);
+  if (cudaMemsetAsync(w.tickets, 0, 4 * C, s) != cudaSuccess) return ACTNN_ERR_LAUNCH;
+  switch (dtype) {
+    case ACTNN_F32:
+      return backward_typed<float>(x, grad_out, weight, mean, invstd, nullptr, grad_weight, sum_dy, sum_dy_xmu, N, C,
+                                   HW, w, S, s);
+    case ACTNN_F16:
+      return backward_typed<__half>(x, grad_out, weight, mean, invstd, nullptr, grad_weight, sum_dy, sum_dy_xmu, N,
+                                    C, HW, w, S, s);
+    case ACTNN_BF16:
+      return backward_typed<__nv_bfloat16>(x, grad_out, weight, mean, invstd, nullptr, grad_weight, sum_dy,
+                                           sum_dy_xmu, N, C, HW, w, S, s);
+    default: return ACTNN_ERR_DTYPE;
+  }
+}
+
+extern "C" int actnn_batch_norm_backward_elemt(const void* x, const void* grad_out, const float* weight,
+                                               const float* mean, const float* invstd, const float* sum_dy,
+                                               const float* sum_dy_xmu, const float* counts, int64_t n_counts,
+                                               void* grad_in,
+                                               int64_t N, int64_t C, int64_t HW, int dtype, void* workspace,
+                                               int64_t workspace_bytes, actnn_stream_t stream) {
+  if (int st = check_shape(N, C, HW)) return st;
+  if (N * C * HW == 0) return ACTNN_OK;
+  if (n_counts <= 0 || n_counts > 65536) return ACTNN_ERR_ARG;
+  if (!x || !grad_out || !grad_in || !mean || !invstd || !sum_dy || !sum_dy_xmu || !counts || !workspace)
+    return ACTNN_ERR_NULL;
+  if (workspace_bytes < 16 * C || !aligned(workspace, 16)) return ACTNN_ERR_CAPACITY;
+  cudaStream_t s = (cudaStream_t)stream;
+  float4* coef = (float4*)workspace;
+  bn_backward_coef_kernel<<<(unsigned)((C + 255) / 256), 256, 0, s>>>(mean, invstd, weight, sum_dy, sum_dy_xmu,
+                                                                       counts, (int)n_counts, coef, (int)C);
+  switch (dtype) {
+    case ACTNN_F32: return backward_apply_typed<float>(x, grad_out, grad_in, coef, N, C, HW, s);
+    case ACTNN_F16: return backward_apply_typed<__half>(x, grad_out, grad_in, coef, N, C, HW, s);
+    case ACTNN_BF16: return backward_apply_typed<__nv_bfloat16>(x, grad_out, grad_in, coef, N, C, HW, s);
     default: return ACTNN_ERR_DTYPE;
   }
 }

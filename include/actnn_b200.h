@@ -282,6 +282,35 @@ int actnn_batch_norm_backward(const void* x, const void* grad_out, const float* 
                               actnn_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * The four halves of a batch norm whose statistics are combined across ranks in between.
+ * Replace the ATen operators the reference's synchronised batch norm calls: batch_norm_stats
+ * (actnn/actnn/ops.py:515), batch_norm_elemt (ops.py:554), batch_norm_backward_reduce
+ * (ops.py:570-577) and batch_norm_backward_elemt (ops.py:594-603).  Same tensors and meanings as those
+ * operators: `mean` / `invstd` are float32 [C]; `sum_dy` = sum of grad_out, `sum_dy_xmu` = sum of
+ * grad_out * (x - mean), `grad_weight` = sum_dy_xmu * invstd (sum_dy doubles as grad_bias);
+ * `counts` = float32 device array of every rank's elements per channel (summed on the device,
+ * so no host read is needed).  y of actnn_batch_norm_forward may be
+ * NULL (statistics only); that is what actnn_batch_norm_stats calls.  Workspace as above
+ * (the element-wise halves use its first 16 * C bytes). */
+int actnn_batch_norm_stats(const void* x, float* mean, float* invstd, int64_t N, int64_t C,
+                           int64_t HW, double eps, int dtype, void* workspace,
+                           int64_t workspace_bytes, actnn_stream_t stream);
+int actnn_batch_norm_elemt(const void* x, const float* weight, const float* bias,
+                           const float* mean, const float* invstd, void* y, int64_t N, int64_t C,
+                           int64_t HW, int dtype, void* workspace, int64_t workspace_bytes,
+                           actnn_stream_t stream);
+int actnn_batch_norm_backward_reduce(const void* x, const void* grad_out, const float* weight,
+                                     const float* mean, const float* invstd, float* sum_dy,
+                                     float* sum_dy_xmu, float* grad_weight, int64_t N, int64_t C,
+                                     int64_t HW, int dtype, void* workspace,
+                                     int64_t workspace_bytes, actnn_stream_t stream);
+int actnn_batch_norm_backward_elemt(const void* x, const void* grad_out, const float* weight,
+                                    const float* mean, const float* invstd, const float* sum_dy,
+                                    const float* sum_dy_xmu, const float* counts, int64_t n_counts,
+                                    void* grad_in, int64_t N, int64_t C, int64_t HW, int dtype,
+                                    void* workspace, int64_t workspace_bytes, actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * How many bulk-copy waits gave up on the current device since the library was loaded.
  * The opt-in staged pack kernels (environment ACTNN_STAGED_PACK=1) copy their inputs into
  * shared memory with the bulk-copy engine and bound every wait on the completion barrier;

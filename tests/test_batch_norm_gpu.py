@@ -117,3 +117,70 @@ def test_batch_norm_module_trains_like_torch(actnn, cuda_device):
     assert torch.allclose(ours.bias.grad, ref.bias.grad, rtol=1e-4, atol=1e-4)
     assert torch.allclose(ours.running_var, ref.running_var, rtol=1e-5, atol=1e-6)
     assert torch.allclose(ours.running_mean, ref.running_mean, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(8, 32, 14, 14), (6, 10, 7, 7), (16, 24)])
+def test_sync_halves_match_the_aten_operators(cuda_device, shape, dtype):
+    """batch_norm_stats / elemt / backward_reduce / backward_elemt against the ATen operators
+    of the same names (the ones the reference's synchronised batch norm calls)."""
+    from actnn_b200.cpp_extension import backward_func as bf
+    x, gy, w, b, _, _ = _inputs(shape, dtype, cuda_device, seed=9)
+    tol = TOL[dtype]
+    mean, invstd = bf.batch_norm_stats(x, 1e-5)
+    mean_t, invstd_t = torch.batch_norm_stats(x, 1e-5)
+    assert _close(mean, mean_t, 1e-5) and _close(invstd, invstd_t, 1e-4)
+    y = bf.batch_norm_elemt(x, w, b, mean_t, invstd_t, 1e-5)
+    assert _close(y, torch.batch_norm_elemt(x, w, b, mean_t, invstd_t, 1e-5), tol)
+    sum_dy, sum_dy_xmu, gw, gb = bf.batch_norm_backward_reduce(gy, x, mean_t, invstd_t, w, True, True, True)
+    sum_dy_t, sum_dy_xmu_t, gw_t, gb_t = torch.batch_norm_backward_reduce(gy, x, mean_t, invstd_t, w, True, True, True)
+    # the sums themselves are checked in float64 (ATen's own float16 sums are off by ~3e-4)
+    dims = [d for d in range(x.dim()) if d != 1]
+    view = [1, -1] + [1] * (x.dim() - 2)
+    sum_dy_64 = gy.double().sum(dim=dims)
+    sum_dy_xmu_64 = (gy.double() * (x.double() - mean_t.double().view(view))).sum(dim=dims)
+    assert _close(sum_dy, sum_dy_64, 2e-5) and _close(sum_dy_xmu, sum_dy_xmu_64, 2e-5)
+    assert _close(gw, sum_dy_xmu_64 * invstd_t.double(), 2e-5) and _close(gb, sum_dy_64, 2e-5)
+    assert _close(sum_dy, sum_dy_t, 2e-3) and _close(gw, gw_t, 2e-3)
+    # two "ranks" with the same batch: sums and counts double
+    per_rank = x.numel() // x.shape[1]
+    count = torch.tensor([per_rank, per_rank], dtype=torch.float32, device=cuda_device)
+    dx = bf.batch_norm_backward_elemt(gy, x, mean_t, invstd_t, w, 2 * sum_dy_t, 2 * sum_dy_xmu_t, count)
+    dx_t = torch.batch_norm_backward_elemt(gy, x, mean_t, invstd_t, w, 2 * sum_dy_t, 2 * sum_dy_xmu_t, count.int())
+    assert _close(dx, dx_t, tol)
+
+
+def test_sync_batch_norm_op_in_a_one_rank_group_matches_batch_norm(actnn, cuda_device):
+    """ops.sync_batch_norm itself (all_gather / all_reduce over a one-rank NCCL group) against
+    nn.BatchNorm2d."""
+    import os
+    import torch.distributed as dist
+    from actnn_b200 import ops
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    created = not dist.is_initialized()
+    if created:
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=cuda_device)
+    try:
+        actnn.set_optimization_level("L0")
+        torch.manual_seed(1)
+        ref = torch.nn.BatchNorm2d(12).to(cuda_device)
+        w = ref.weight.detach().clone().requires_grad_(True)
+        b = ref.bias.detach().clone().requires_grad_(True)
+        rm, rv = ref.running_mean.clone(), ref.running_var.clone()
+        x = torch.randn(6, 12, 9, 9, device=cuda_device)
+        xr, xo = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        yr = ref(xr)
+        yo = ops.sync_batch_norm.apply(xo, w, b, rm, rv, ref.eps, ref.momentum, dist.group.WORLD, 1, None)
+        gy = torch.randn_like(yr)
+        yr.backward(gy)
+        yo.backward(gy)
+        assert torch.allclose(yo, yr, rtol=1e-4, atol=1e-5)
+        assert torch.allclose(xo.grad, xr.grad, rtol=1e-4, atol=1e-5)
+        assert torch.allclose(w.grad, ref.weight.grad, rtol=1e-4, atol=1e-4)
+        assert torch.allclose(b.grad, ref.bias.grad, rtol=1e-4, atol=1e-4)
+        assert torch.allclose(rv, ref.running_var, rtol=1e-5, atol=1e-6)
+        assert torch.allclose(rm, ref.running_mean, rtol=1e-5, atol=1e-6)
+    finally:
+        if created:
+            dist.destroy_process_group()
