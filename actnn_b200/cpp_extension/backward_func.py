@@ -114,17 +114,22 @@ def cudnn_batch_norm_backward(input, grad_output, weight, running_mean, running_
     return dx, dweight, dbias
 
 
-def batch_norm_stats(input, eps):
+def batch_norm_stats(input, eps, out=None):
     """``torch.batch_norm_stats``: per-channel ``(mean, invstd)`` of this rank's batch
-    (reference call site: ops.py:515)."""
+    (reference call site: ops.py:515).  ``out``: an optional contiguous float32 buffer of at
+    least ``2 * C`` elements that receives mean then invstd (the message a synchronised batch
+    norm gathers), so that no concatenation is needed."""
     x = input.contiguous()
     N, C, HW = _bn_dims(x)
-    mean = torch.empty(C, dtype=torch.float32, device=x.device)
-    invstd = torch.empty(C, dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty(2 * C, dtype=torch.float32, device=x.device)
+    elif out.dtype != torch.float32 or not out.is_contiguous() or out.numel() < 2 * C or out.device != x.device:
+        raise RuntimeError("batch_norm_stats: out must be a contiguous float32 tensor of >= 2*C elements")
     ws, nbytes = _bn_workspace(N, C, HW, x.device)
-    _lib.call("actnn_batch_norm_stats", x, _lib.ptr(x), _lib.ptr(mean), _lib.ptr(invstd), N, C, HW, float(eps),
+    _lib.call("actnn_batch_norm_stats", x, _lib.ptr(x), out.data_ptr(), out.data_ptr() + 4 * C, N, C, HW, float(eps),
               _lib.dtype_id(x.dtype), _lib.ptr(ws), nbytes, _lib.stream_of(x))
-    return mean, invstd
+    flat = out.view(-1)
+    return flat[:C], flat[C:2 * C]
 
 
 def batch_norm_elemt(input, weight, bias, mean, invstd, eps):
@@ -139,25 +144,31 @@ def batch_norm_elemt(input, weight, bias, mean, invstd, eps):
     return y
 
 
-def batch_norm_backward_reduce(grad_out, input, mean, invstd, weight, input_g, weight_g, bias_g):
+def batch_norm_backward_reduce(grad_out, input, mean, invstd, weight, input_g, weight_g, bias_g, out=None):
     """``torch.batch_norm_backward_reduce``: ``(sum_dy, sum_dy_xmu, grad_weight, grad_bias)`` of this
-    rank (ops.py:570-577)."""
+    rank (ops.py:570-577).  ``out``: optional contiguous float32 ``[2 * C]`` buffer that receives
+    sum_dy then sum_dy_xmu (the message a synchronised batch norm all-reduces)."""
     x = input.contiguous()
     dy = grad_out.contiguous()
     if dy.dtype != x.dtype:
         dy = dy.to(x.dtype)
     N, C, HW = _bn_dims(x)
-    sum_dy = torch.empty(C, dtype=torch.float32, device=x.device)
-    sum_dy_xmu = torch.empty(C, dtype=torch.float32, device=x.device)
+    if out is None:
+        out = torch.empty(2 * C, dtype=torch.float32, device=x.device)
+    elif out.dtype != torch.float32 or not out.is_contiguous() or out.numel() < 2 * C or out.device != x.device:
+        raise RuntimeError("batch_norm_backward_reduce: out must be a contiguous float32 tensor of >= 2*C elements")
     grad_weight = torch.empty(C, dtype=torch.float32, device=x.device)
     ws, nbytes = _bn_workspace(N, C, HW, x.device)
     _lib.call("actnn_batch_norm_backward_reduce", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(_as_f32(weight)),
-              _lib.ptr(_as_f32(mean)), _lib.ptr(_as_f32(invstd)), _lib.ptr(sum_dy), _lib.ptr(sum_dy_xmu),
+              _lib.ptr(_as_f32(mean)), _lib.ptr(_as_f32(invstd)), out.data_ptr(), out.data_ptr() + 4 * C,
               _lib.ptr(grad_weight), N, C, HW, _lib.dtype_id(x.dtype), _lib.ptr(ws), nbytes, _lib.stream_of(x))
-    grad_bias = sum_dy
+    flat = out.view(-1)
+    sum_dy, sum_dy_xmu = flat[:C], flat[C:2 * C]
+    grad_bias = sum_dy.clone() if bias_g else None             # the message buffer is all-reduced in place later
     if weight is not None and weight.dtype != torch.float32:
-        grad_weight, grad_bias = grad_weight.to(weight.dtype), grad_bias.to(weight.dtype)
-    return sum_dy, sum_dy_xmu, (grad_weight if weight_g else None), (grad_bias if bias_g else None)
+        grad_weight = grad_weight.to(weight.dtype)
+        grad_bias = None if grad_bias is None else grad_bias.to(weight.dtype)
+    return sum_dy, sum_dy_xmu, (grad_weight if weight_g else None), grad_bias
 
 
 def batch_norm_backward_elemt(grad_out, input, mean, invstd, weight, sum_dy, sum_dy_xmu, count):

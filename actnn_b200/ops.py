@@ -434,21 +434,22 @@ class sync_batch_norm(Function):
     def forward(self, input, weight, bias, running_mean, running_var, eps, momentum, process_group, world_size,
                 scheme):
         input = input.contiguous()
-        count = torch.full((1,), input.numel() // input.size(1), dtype=running_mean.dtype, device=input.device)
-        mean, invstd = ext_backward_func.batch_norm_stats(input, eps)
         num_channels = input.shape[1]
-        combined = torch.cat([mean, invstd, count], dim=0)                   # [2C + 1]
-        gathered = [torch.empty_like(combined) for _ in range(world_size)]
-        dist.all_gather(gathered, combined, process_group, async_op=False)
-        combined = torch.stack(gathered, dim=0)                              # [world, 2C + 1]
-        mean_all, invstd_all, count_all = torch.split(combined, num_channels, dim=1)
+        local_count = input.numel() // num_channels
+        # the gathered message [mean, invstd, count] is written in place: no cat / stack
+        combined = torch.empty(2 * num_channels + 1, dtype=torch.float32, device=input.device)
+        ext_backward_func.batch_norm_stats(input, eps, out=combined)
+        combined[2 * num_channels:].fill_(local_count)
+        gathered = torch.empty(world_size, 2 * num_channels + 1, dtype=torch.float32, device=input.device)
+        dist.all_gather_into_tensor(gathered, combined, process_group, async_op=False)
+        mean_all, invstd_all, count_all = torch.split(gathered, num_channels, dim=1)
         # every rank contributes at least one value per channel, so the reference's check
         # (ops.py:530-533) can only trip in a single-rank group: no device read is needed
-        size = input.numel() // input.size(1) if world_size == 1 else 2
+        size = local_count if world_size == 1 else 2
         if size == 1:
             raise ValueError("Expected more than 1 value per channel when training, got input size {}".format(size))
         mean, invstd = torch.batch_norm_gather_stats_with_counts(
-            input, mean_all, invstd_all, running_mean, running_var, momentum, eps, count_all.view(-1))
+            input, mean_all, invstd_all, running_mean, running_var, momentum, eps, count_all.reshape(-1))
 
         self.saved = quantize_activation(input, scheme)
         self.save_for_backward(weight, mean, invstd, count_all)
@@ -465,16 +466,15 @@ class sync_batch_norm(Function):
         del self.saved
         weight, mean, invstd, count_tensor = self.saved_tensors
         grad_input = None
+        num_channels = saved_input.shape[1]
+        combined = torch.empty(2 * num_channels, dtype=torch.float32, device=saved_input.device)
         sum_dy, sum_dy_xmu, grad_weight, grad_bias = ext_backward_func.batch_norm_backward_reduce(
             grad_output, saved_input, mean, invstd, weight, self.needs_input_grad[0], self.needs_input_grad[1],
-            self.needs_input_grad[2])
+            self.needs_input_grad[2], out=combined)
         if self.needs_input_grad[0]:
-            num_channels = sum_dy.shape[0]
-            combined = torch.cat([sum_dy, sum_dy_xmu], dim=0)
             dist.all_reduce(combined, dist.ReduceOp.SUM, self.process_group, async_op=False)
-            sum_dy, sum_dy_xmu = torch.split(combined, num_channels)
             grad_input = ext_backward_func.batch_norm_backward_elemt(
-                grad_output, saved_input, mean, invstd, weight, sum_dy, sum_dy_xmu, count_tensor.view(-1))
+                grad_output, saved_input, mean, invstd, weight, sum_dy, sum_dy_xmu, count_tensor.reshape(-1))
         if weight is None or not self.needs_input_grad[1]:
             grad_weight = None
         if weight is None or not self.needs_input_grad[2]:
