@@ -29,6 +29,7 @@ class QuantizationConfig:
         self.pipeline_threshold = None
         self.cudnn_benchmark_conv2d = True
         self.swap = False
+        self.swap_arena = True                 # pooled pinned buffers + copy streams for the swap (False: the reference's scheme)
 
         # debugging
         self.debug_memory_model = ast.literal_eval(os.environ.get("DEBUG_MEM", "False"))

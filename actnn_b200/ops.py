@@ -28,7 +28,7 @@ from .cpp_extension import backward_func as ext_backward_func
 from .cpp_extension import minimax as ext_minimax
 from .cpp_extension import quantization as ext_quantization
 from .qscheme import group_minimax, to_groups
-from .utils import compute_tensor_bytes, empty_cache, get_memory_usage, swap_to_cpu
+from .utils import compute_tensor_bytes, empty_cache, get_memory_usage, swap_to_cpu, swap_to_gpu
 
 QParams = namedtuple("QParams", ["range", "zero_point", "num_bits"])
 
@@ -74,10 +74,7 @@ def dequantize_and_unpack(data, shape, bits, scale, mn, out_dtype=None):
     if config.simulate:
         return data / scale + mn
     if config.swap:
-        offsets = getattr(data, "word_offsets", None)
-        data = data.cuda(non_blocking=True)
-        if offsets is not None:
-            data.word_offsets = offsets
+        data = swap_to_gpu(data)
     N = shape[0]
     num_features = int(np.prod(shape[1:]))
     gs = config.group_size
@@ -144,7 +141,7 @@ def dequantize_activation(quantized, q_input_shape, dtype=None):
     if not config.compress_activation:
         ret = quantized[0]
         if config.swap:
-            ret = ret.cuda(non_blocking=True)
+            ret = swap_to_gpu(ret)
         return ret
 
     q_input, q_bits, q_scale, q_min = quantized

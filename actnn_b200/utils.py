@@ -8,14 +8,34 @@ import numpy as np
 import torch
 
 
-def swap_to_cpu(tensor: torch.Tensor) -> torch.Tensor:
-    """Asynchronous copy into freshly pinned host memory."""
-    host = torch.empty(tensor.shape, dtype=tensor.dtype, device="cpu", pin_memory=True)
+def swap_to_cpu(tensor: torch.Tensor):
+    """Move a saved tensor to pinned host memory (reference: utils.py:10-16).
+
+    With ``config.swap_arena`` (the default) the copy goes through the pooled arena of
+    ``swap_arena.py`` on a copy stream and a ``SwappedTensor`` handle comes back; otherwise
+    this is the reference's scheme: an asynchronous copy into freshly pinned memory."""
+    from .conf import config
+    if tensor.is_cuda and getattr(config, "swap_arena", True):
+        from .swap_arena import arena_for
+        return arena_for(tensor.device).to_host(tensor)
+    host = torch.empty(tensor.shape, dtype=tensor.dtype, device="cpu", pin_memory=tensor.is_cuda)
     host.copy_(tensor, non_blocking=True)
     for attr in ("word_offsets",):
         if hasattr(tensor, attr):
             setattr(host, attr, getattr(tensor, attr))
     return host
+
+
+def swap_to_gpu(saved):
+    """The CUDA tensor behind what ``swap_to_cpu`` returned, usable on the current stream."""
+    from .swap_arena import SwappedTensor
+    if isinstance(saved, SwappedTensor):
+        return saved.arena.to_device(saved)
+    out = saved.cuda(non_blocking=True)
+    offsets = getattr(saved, "word_offsets", None)
+    if offsets is not None:
+        out.word_offsets = offsets
+    return out
 
 
 def get_memory_usage(print_info: bool = False) -> int:

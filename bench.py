@@ -491,6 +491,8 @@ def run_resnet(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     steps, warm = max(3, min(args.steps, 30)), max(3, min(args.warmup, 5))
+    if args.level in ("L4", "L5", "swap"):
+        warm = max(warm, 8)          # the pinned pool of the host swap fills while the per-layer widths settle
     res = {}
     for level in ("exact", args.level):
         res[level] = resnet_throughput(level, args.batch, steps, warm, dev, world, args.arch, args.amp)
