@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this folder by running the REFERENCE's own Python code.
 
-Run once, in a container that has the reference checkout (default ``/root/reference``):
+Run once, in a container that has the reference checkout (its root in ``ACTNN_REFERENCE_ROOT``):
 
     python oracle/build_ref.py            # the reference's calc_precision.cc, unmodified
     python tests/golden/make_golden.py
