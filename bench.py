@@ -478,10 +478,62 @@ def resnet_throughput(level: str, batch: int, steps: int, warmup: int, dev, worl
             "activation_bytes": int(act_bytes), "peak_bytes": int(peak)}
 
 
+def resnet_kernel_table(args):
+    """`--workload resnet --kernel-table`: GPU time of three training steps by kernel (torch
+    profiler, CUPTI), printed as a table.  A diagnostic, not a bench value."""
+    import torch
+    import torch.nn as nn
+    import torchvision
+    from torch.profiler import ProfilerActivity, profile
+
+    import actnn_b200 as actnn
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    if args.level != "exact":
+        actnn.set_optimization_level(args.level)
+    model = getattr(torchvision.models, args.arch)()
+    if args.level != "exact":
+        model = actnn.QModule(model)
+    model = model.to(dev).train()
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    dt = getattr(torch, args.amp)
+    scaler = torch.amp.GradScaler("cuda", enabled=dt == torch.float16)
+    crit = nn.CrossEntropyLoss()
+    images = torch.randn(args.batch, 3, 224, 224, device=dev)
+    target = torch.randint(0, 1000, (args.batch,), device=dev)
+
+    def step():
+        with torch.autocast("cuda", dtype=dt):
+            loss = crit(model(images), target)
+        opt.zero_grad(set_to_none=True)
+        scaler.scale(loss).backward()
+        scaler.step(opt)
+        scaler.update()
+
+    for _ in range(4):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+    rows = sorted(prof.key_averages(), key=lambda e: -e.self_device_time_total)
+    total = sum(e.self_device_time_total for e in rows)
+    print("GPU time of 3 steps: %.1f ms (%.1f ms per step)" % (total / 1e3, total / 3e3))
+    print("| kernel | launches | total ms | avg us | share |\n|---|---|---|---|---|")
+    for e in rows[:30]:
+        print("| `%s` | %d | %.2f | %.1f | %.1f%% |" % (e.key[:90], e.count, e.self_device_time_total / 1e3,
+                                                     e.self_device_time_total / max(e.count, 1),
+                                                     100.0 * e.self_device_time_total / max(total, 1)))
+
+
 def run_resnet(args):
     """`--workload resnet50`: whole-job images/s of L3 training next to exact training."""
     import torch
     import torch.distributed as dist
+
+    if args.kernel_table:
+        return resnet_kernel_table(args)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -616,6 +668,8 @@ def main():
     ap.add_argument("--level", default="L3")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--amp", default="float16", choices=["float16", "bfloat16"])
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="with --workload resnet: print GPU time by kernel for three steps (torch profiler)")
     ap.add_argument("--profile", default=None, help="run a few launches of one kernel (for ncu); 'all' = each")
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--gpus", type=int, default=1)
