@@ -56,11 +56,58 @@ max_pool_forward_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t* __re
   }
 }
 
+// Forward for K x K windows with K known at compile time and unit dilation: the K*K taps
+// are loaded unconditionally (coordinates clamped into the plane, validity kept aside) so
+// that all loads of a window are in flight together; the scan order and the strict
+// comparison are those of the general kernel.
+template <typename T, int K>
+__global__ void __launch_bounds__(256)
+max_pool_forward_fixed_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t* __restrict__ idx, int planes,
+                              PoolGeom g) {
+  const int plane_elems = g.H * g.W, out_elems = g.Ho * g.Wo;
+  for (int nc = blockIdx.y; nc < planes; nc += gridDim.y) {
+    const T* plane = x + (int64_t)nc * plane_elems;
+    T* y_p = y + (int64_t)nc * out_elems;
+    int8_t* idx_p = idx + (int64_t)nc * out_elems;
+    for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < out_elems; o += gridDim.x * blockDim.x) {
+      const int ho = o / g.Wo, wo = o - ho * g.Wo;
+      const int hb = ho * g.SH - g.PH, wb = wo * g.SW - g.PW;
+      float v[K * K];
+      bool ok[K * K];
+#pragma unroll
+      for (int kh = 0; kh < K; ++kh) {
+        const int h = hb + kh;
+        const bool hok = h >= 0 && h < g.H;
+        const int hc = min(max(h, 0), g.H - 1);
+#pragma unroll
+        for (int kw = 0; kw < K; ++kw) {
+          const int w = wb + kw;
+          ok[kh * K + kw] = hok && w >= 0 && w < g.W;
+          v[kh * K + kw] = load_scalar<T>(plane, hc * g.W + min(max(w, 0), g.W - 1));
+        }
+      }
+      float best = -INFINITY;
+      int arg = 0;
+#pragma unroll
+      for (int t = 0; t < K * K; ++t)
+        if (ok[t] && v[t] > best) { best = v[t]; arg = t; }
+      store_scalar<T>(y_p, o, best);
+      idx_p[o] = (int8_t)arg;
+    }
+  }
+}
+
 template <typename T>
 int launch_forward(const void* x, void* y, int8_t* idx, int64_t planes, const PoolGeom& g, cudaStream_t s) {
   const int out_elems = g.Ho * g.Wo;
   dim3 grid = plane_grid(out_elems, planes);
-  max_pool_forward_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (T*)y, idx, (int)planes, g);
+  const bool unit = g.DH == 1 && g.DW == 1 && g.KH == g.KW;
+  if (unit && g.KH == 3)
+    max_pool_forward_fixed_kernel<T, 3><<<grid, 256, 0, s>>>((const T*)x, (T*)y, idx, (int)planes, g);
+  else if (unit && g.KH == 2)
+    max_pool_forward_fixed_kernel<T, 2><<<grid, 256, 0, s>>>((const T*)x, (T*)y, idx, (int)planes, g);
+  else
+    max_pool_forward_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (T*)y, idx, (int)planes, g);
   return check_launch();
 }
 
@@ -106,12 +153,120 @@ max_pool_backward_kernel(const T* __restrict__ gy, const int8_t* __restrict__ id
   }
 }
 
+// Backward by row segments (unit dilation, at most two window rows over an input row, at most
+// NWIN window columns over eight neighbouring positions: every pooling layer of the usual
+// networks).  A thread owns eight consecutive positions of one input row.  It loads the
+// arg-max code and the gradient of all 2 x NWIN candidate windows unconditionally (clamped
+// coordinates, validity aside), so that the loads are in flight together, decodes each code
+// into (kh, kw) with two 16-entry nibble tables, and adds the gradient to the position the
+// window selected if that lies in its segment.  Index arithmetic is paid once per eight
+// outputs, the store is one 16-byte vector when the row allows it, and every position
+// receives its terms in the general kernel's order (window rows, then columns, ascending).
+template <typename T, int NWIN>
+__global__ void __launch_bounds__(256)
+max_pool_backward_row_kernel(const T* __restrict__ gy, const int8_t* __restrict__ idx, T* __restrict__ gx,
+                             uint32_t total_segments, int segs_per_row, PoolGeom g, uint64_t kh_of, uint64_t kw_of,
+                             int vector_store) {
+  const int out_elems = g.Ho * g.Wo, plane_elems = g.H * g.W;
+  const int reach_h = g.KH - 1, reach_w = g.KW - 1;
+  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < total_segments; t += gridDim.x * blockDim.x) {
+    const uint32_t row = t / (uint32_t)segs_per_row;
+    const int seg = (int)(t - row * (uint32_t)segs_per_row);
+    const uint32_t nc = row / (uint32_t)g.H;
+    const int h = (int)(row - nc * (uint32_t)g.H);
+    const int w0 = seg * 8;
+    const int last = min(w0 + 7, g.W - 1);
+    const T* gy_p = gy + (int64_t)nc * out_elems;
+    const int8_t* idx_p = idx + (int64_t)nc * out_elems;
+    const int ah = h + g.PH, aw0 = w0 + g.PW;
+    const int ho_hi = min(g.Ho - 1, ah / g.SH);
+    const int ho_lo = ah > reach_h ? (ah - reach_h + g.SH - 1) / g.SH : 0;
+    const int wo_hi = min(g.Wo - 1, (last + g.PW) / g.SW);
+    const int wo_lo = aw0 > reach_w ? (aw0 - reach_w + g.SW - 1) / g.SW : 0;
+    int code[2][NWIN];
+    float grad[2][NWIN];
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const int hoc = min(ho_lo + a, g.Ho - 1);
+#pragma unroll
+      for (int b = 0; b < NWIN; ++b) {
+        const int o = hoc * g.Wo + min(wo_lo + b, g.Wo - 1);
+        code[a][b] = idx_p[o];
+        grad[a][b] = load_scalar<T>(gy_p, o);
+      }
+    }
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const int ho = ho_lo + a;
+      const int kh_need = ah - ho * g.SH;                        // the tap row this input row is in that window row
+#pragma unroll
+      for (int b = 0; b < NWIN; ++b) {
+        const int wo = wo_lo + b;
+        const int c = code[a][b] & 15;
+        const int kh = (int)((kh_of >> (4 * c)) & 15), kw = (int)((kw_of >> (4 * c)) & 15);
+        const bool live = ho <= ho_hi && wo <= wo_hi && kh == kh_need;
+        const int target = live ? wo * g.SW - g.PW + kw - w0 : -1;   // position inside the segment
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += target == j ? grad[a][b] : 0.f;
+      }
+    }
+    T* out = gx + (int64_t)nc * plane_elems + h * g.W + w0;
+    if (vector_store) {                                        // W % 8 == 0 and a 16-byte aligned tensor
+      if constexpr (sizeof(T) == 2) {
+        uint4 v;
+        uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          T lo, hi;
+          store_scalar<T>(&lo, 0, acc[2 * k]);
+          store_scalar<T>(&hi, 0, acc[2 * k + 1]);
+          pv[k] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&lo)) |
+                  ((uint32_t)(*reinterpret_cast<const uint16_t*>(&hi)) << 16);
+        }
+        *reinterpret_cast<uint4*>(out) = v;
+      } else {
+        *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (w0 + j < g.W) store_scalar<T>(out, j, acc[j]);
+    }
+  }
+}
+
 template <typename T>
 int launch_backward(const void* gy, const int8_t* idx, void* gx, int64_t planes, const PoolGeom& g, cudaStream_t s) {
   const int plane_elems = g.H * g.W;
-  dim3 grid = plane_grid(plane_elems, planes);
   const bool unit = g.DH == 1 && g.DW == 1;
   const int p = (int)planes;
+  // window columns that can touch eight neighbouring positions: positions aw0 .. aw0 + 7 see
+  // columns ceil((aw0 - (KW-1)) / SW) .. floor((aw0 + 7) / SW), at most (7 + KW-1) / SW + 1 of them
+  const int nwin = (7 + g.KW - 1) / g.SW + 1;
+  const int segs = (g.W + 7) / 8;
+  const int64_t total_segments = planes * g.H * segs;
+  if (unit && (g.KH + g.SH - 1) / g.SH <= 2 && nwin <= 10 && total_segments < ((int64_t)1 << 31)) {
+    uint64_t kh_of = 0, kw_of = 0;                               // code -> (kh, kw), one nibble each
+    for (int c = 0; c < g.KH * g.KW; ++c) {
+      kh_of |= (uint64_t)(c / g.KW) << (4 * c);
+      kw_of |= (uint64_t)(c % g.KW) << (4 * c);
+    }
+    const int vec = g.W % 8 == 0 && aligned(gx, 16);
+    const int64_t blocks = (total_segments + 255) / 256;
+    const int grid = (int)max((int64_t)1, min(blocks, (int64_t)device_info().sm_count * 16));
+    if (nwin <= 6)
+      max_pool_backward_row_kernel<T, 6><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, (uint32_t)total_segments,
+                                                              segs, g, kh_of, kw_of, vec);
+    else
+      max_pool_backward_row_kernel<T, 10><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, (uint32_t)total_segments,
+                                                               segs, g, kh_of, kw_of, vec);
+    return check_launch();
+  }
+  dim3 grid = plane_grid(plane_elems, planes);
   if (unit && g.SH == 2 && g.SW == 2)
     max_pool_backward_kernel<T, 2, true><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, p, g);
   else if (unit && g.SH == 1 && g.SW == 1)

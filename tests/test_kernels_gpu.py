@@ -290,7 +290,10 @@ def test_dropout_forward_backward(ext, dtype):
 @pytest.mark.parametrize("geom", [((4, 8, 28, 28), (3, 3), (2, 2), (1, 1), (1, 1)),
                                   ((2, 3, 17, 9), (2, 2), (2, 2), (0, 0), (1, 1)),
                                   ((1, 2, 12, 13), (3, 2), (1, 2), (1, 0), (1, 1)),
-                                  ((2, 2, 15, 15), (3, 3), (2, 2), (1, 1), (2, 2))])
+                                  ((2, 2, 15, 15), (3, 3), (2, 2), (1, 1), (2, 2)),
+                                  ((2, 4, 16, 32), (3, 3), (2, 2), (1, 1), (1, 1)),     # vector stores
+                                  ((2, 2, 16, 16), (2, 2), (1, 1), (0, 0), (1, 1)),     # stride 1: ten columns
+                                  ((1, 3, 9, 40), (2, 3), (2, 3), (1, 1), (1, 1))])
 def test_max_pool2d_forward_backward(ext, dtype, geom):
     shape, k, s, p, d = geom
     x = make_input(shape, dtype, sum(shape))
