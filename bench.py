@@ -13,7 +13,8 @@ bits, two 2-byte statistics per 256-element group) = 232.8 MB per step.
 The printed JSON line carries
   value       device-resident throughput (inputs in HBM, raw C-ABI calls, CUDA-event timed);
   e2e         the same work through the public Python API from pinned HOST buffers:
-              H2D copy -> quantize_activation -> dequantize_activation -> D2H copy;
+              H2D copy -> quantize_activation -> dequantize_activation -> D2H copy, three steps in
+              flight on three streams so that uploads, kernels and downloads overlap;
   roofline    the dominant kernel (fused compress) against the measured HBM copy peak;
   kernels     per-kernel GB/s for the other kernels of the path (informational);
   cpu_baseline  the CPU oracle (a restatement of the reference's simulate path) timed on the
@@ -348,27 +349,48 @@ def run_ours(args):
     actnn.set_optimization_level("L2")                      # uniform width, no adaptive scheme
     actnn.config.activation_compression_bits = [bits]
     shape = (N, C, H, W)
-    host_in = [torch.randn(shape, dtype=dt).pin_memory() for _ in range(2)]
-    host_out = [torch.empty(shape, dtype=dt).pin_memory() for _ in range(2)]
-    dev_in = torch.empty(shape, dtype=dt, device=dev)
+    # Three steps are in flight at once, each on its own stream with its own buffers, so that the
+    # upload of one step overlaps the download of the previous one (PCIe is full duplex) and the
+    # kernels of the one in between.  Every step still uploads its input and downloads its result.
+    LANES = 3
+    host_in = [torch.randn(shape, dtype=dt).pin_memory() for _ in range(LANES)]
+    host_out = [torch.empty(shape, dtype=dt).pin_memory() for _ in range(LANES)]
+    dev_in = [torch.empty(shape, dtype=dt, device=dev) for _ in range(LANES)]
+    lanes = [torch.cuda.Stream(dev) for _ in range(LANES)]
 
     def e2e_step(k):
-        dev_in.copy_(host_in[k % 2], non_blocking=True)
-        q = actnn.ops.quantize_activation(dev_in, None)
-        y = actnn.ops.dequantize_activation(q, shape, dt)
-        host_out[k % 2].copy_(y, non_blocking=True)
+        lane = k % LANES
+        with torch.cuda.stream(lanes[lane]):
+            dev_in[lane].copy_(host_in[lane], non_blocking=True)
+            q = actnn.ops.quantize_activation(dev_in[lane], None)
+            y = actnn.ops.dequantize_activation(q, shape, dt)
+            host_out[lane].copy_(y, non_blocking=True)
+            y.record_stream(lanes[lane])
 
-    for k in range(3):
-        e2e_step(k)
-    e2e_steps = max(3, min(args.steps, 20))
+    def e2e_run(count):
+        cur = torch.cuda.current_stream(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(cur)
+        for lane in lanes:
+            lane.wait_event(a)
+        for k in range(count):
+            e2e_step(k)
+        for lane in lanes:
+            done = torch.cuda.Event()
+            done.record(lane)
+            cur.wait_event(done)
+        b.record(cur)
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b)
+
+    e2e_run(2 * LANES)
+    e2e_steps = max(2 * LANES, min(args.steps, 24))
     barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for k in range(e2e_steps):
-        e2e_step(k)
-    b.record()
+    e2e_total_ms = e2e_run(e2e_steps)
     barrier()
-    e2e_ms = a.elapsed_time(b) / e2e_steps
+    # the last download must have delivered the decoded activation
+    assert bool(torch.isfinite(host_out[(e2e_steps - 1) % LANES].float()).all())
+    e2e_ms = e2e_total_ms / e2e_steps
     e2e_ms = max_over_ranks(e2e_ms, dev)
     e2e_value = whole_job_gbs(step_bytes, world, e2e_ms)
 
@@ -394,7 +416,8 @@ def run_ours(args):
                        % (POOL, POOL * elements * 2 / 1e6, POOL // 2), "parallelism": "replicas x%d" % world},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": elements * 2,
                     "d2h_bytes_per_step": elements * 2, "ms_per_step": round(e2e_ms, 4),
-                    "path": "pinned host -> H2D -> ops.quantize_activation -> ops.dequantize_activation -> D2H"},
+                    "path": "pinned host -> H2D -> ops.quantize_activation -> ops.dequantize_activation -> D2H, "
+                            "three steps in flight on three streams"},
             "gpu_launches": 2 * args.steps, "launch_mode": "the K steps replayed from one CUDA graph",
             "roofline": {"kernel": "pack_single_kernel<half, 2 bit, fused> (actnn_compress_single)", "bound": "hbm",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
