@@ -174,18 +174,22 @@ class QScheme(object):
                     layer.bits = means[i]
 
     def if_allocate_perlayer(self):
-        if not config.perlayer:
+        """Called at the end of every layer's backward; re-allocates the per-layer widths when
+        backward has reached the first trainable layer (qscheme.py:130-147 of the reference).
+        The cheap test (is this that layer?) comes first: the scans below are O(layers)."""
+        if not config.perlayer or not (config.compress_activation and config.training):
             return
-        for layer in QScheme.layers:
-            if layer.C is None:
-                return
         first_layer = None
         for layer in QScheme.layers:
             if layer.layer.weight.requires_grad:
                 first_layer = layer
                 break
         # backward reaches the first trainable layer last: re-allocate there
-        if config.compress_activation and config.training and self is first_layer:
-            from .qbnscheme import QBNScheme
-            QScheme.allocate_perlayer()
-            QBNScheme.allocate_perlayer()
+        if self is not first_layer:
+            return
+        for layer in QScheme.layers:
+            if layer.C is None:
+                return
+        from .qbnscheme import QBNScheme
+        QScheme.allocate_perlayer()
+        QBNScheme.allocate_perlayer()
