@@ -57,7 +57,10 @@ struct BundleWalker {
 // Groups per pack bundle: eight octets per lane for 16-bit types, four for float32.
 template <typename T> struct PackShape { static constexpr int GPB = sizeof(T) == 2 ? 8 : 4; };
 
-template <typename T, typename ST, int B, bool FULL>
+// PHILOX (whole bundles): the noise is known at compile time to come from the generator, so
+// the body has no branch on `stochastic` / `noise` and the generator's dependent chain can be
+// interleaved with the arithmetic of neighbouring groups.
+template <typename T, typename ST, int B, bool FULL, bool PHILOX>
 ACTNN_DEV void pack_bundle(const Oct<T> (&x)[PackShape<T>::GPB], const BundleCoord& c, const T* __restrict__ mn,
                            const T* __restrict__ mx, ST* __restrict__ scale, ST* __restrict__ mn_out,
                            int32_t* __restrict__ out, const T* __restrict__ noise, int stochastic,
@@ -83,7 +86,10 @@ ACTNN_DEV void pack_bundle(const Oct<T> (&x)[PackShape<T>::GPB], const BundleCoo
     const QP<T> qp = fetch_params<T>(mine, gi);
     if (FULL || gi < count) {
       Oct<T> nz;
-      if (!stochastic) nz = zero_oct<T>();
+      if constexpr (PHILOX) {
+        if (gi % NoiseShape<T>::GPC == 0) noise_block<T>(gen.key, (uint64_t)(c.q0 + gi), lane, nzb);
+        nz = nzb[gi % NoiseShape<T>::GPC];
+      } else if (!stochastic) nz = zero_oct<T>();
       else if (noise) nz = load_oct<T>(noise + (c.q0 + gi) * kGroup + lane * kOct);
       else if (!FULL) nz = gen.get((uint64_t)(c.q0 + gi));
       else {                                          // FULL: q0 is a multiple of the groups per call
@@ -113,8 +119,8 @@ ACTNN_DEV void pack_bundle(const Oct<T> (&x)[PackShape<T>::GPB], const BundleCoo
   }
 }
 
-template <typename T, typename ST, bool FULL>
-__global__ void __launch_bounds__(kThreads, MagicInfo<T>::paired ? 3 : 2)
+template <typename T, typename ST, bool FULL, bool PHILOX = false>
+__global__ void __launch_bounds__(kThreads, (MagicInfo<T>::paired && !PHILOX) ? 3 : 2)
 pack_mixed_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T* __restrict__ mx,
                   const int32_t* __restrict__ bits, const int64_t* __restrict__ word_offsets,
                   int32_t* __restrict__ packed, ST* __restrict__ scale, ST* __restrict__ mn_out,
@@ -136,7 +142,7 @@ pack_mixed_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T*
     int32_t* out = packed + (__ldg(word_offsets + c.n) + (int64_t)c.g0 * 8 * b);
 #define ACTNN_CASE(B)                                                                                     \
     case B:                                                                                               \
-      pack_bundle<T, ST, B, FULL>(x, c, mn, mx, scale, mn_out, out, noise, stochastic, gen, plan, lane);  \
+      pack_bundle<T, ST, B, FULL, PHILOX>(x, c, mn, mx, scale, mn_out, out, noise, stochastic, gen, plan, lane); \
       break;
     switch (b) {
       ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
@@ -337,7 +343,12 @@ int launch_pack(const void* data, const void* mn, const void* mx, const int32_t*
   constexpr int GPB = PackShape<T>::GPB;
   const int64_t tasks = N * ((G + GPB - 1) / GPB);
   const NoiseKey key = make_noise_key(seed, offset);
-  if (G % GPB == 0)
+  if (G % GPB == 0 && stochastic && !noise)
+    pack_mixed_kernel<T, ST, true, true><<<persistent_grid(pack_mixed_kernel<T, ST, true, true>, kThreads, tasks),
+                                           kThreads, 0, stream>>>(
+        (const T*)data, (const T*)mn, (const T*)mx, bits, word_offsets, packed, (ST*)scale, (ST*)mn_out, N, G,
+        (const T*)noise, stochastic, key);
+  else if (G % GPB == 0)
     pack_mixed_kernel<T, ST, true><<<persistent_grid(pack_mixed_kernel<T, ST, true>, kThreads, tasks), kThreads, 0,
                                      stream>>>(
         (const T*)data, (const T*)mn, (const T*)mx, bits, word_offsets, packed, (ST*)scale, (ST*)mn_out, N, G,

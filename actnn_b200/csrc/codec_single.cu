@@ -89,8 +89,11 @@ template <typename T, int BITS> struct TaskShape {
 // counted in bytes on one mbarrier per stage.  No register waits on DRAM, so the integer
 // pipe stays fed.
 constexpr int kStages = 2;
-template <typename T, typename ST, int BITS, bool FUSED, bool FULL, bool STAGED>
-__global__ void __launch_bounds__(kThreads, MagicInfo<T>::paired ? 3 : 2)
+// PHILOX (whole tasks, direct loads): the noise is known at compile time to come from the
+// generator, so the body of a round has no branch on `stochastic` / `noise` and the compiler
+// can interleave the generator's dependent chain with the arithmetic of neighbouring octets.
+template <typename T, typename ST, int BITS, bool FUSED, bool FULL, bool STAGED, bool PHILOX = false>
+__global__ void __launch_bounds__(kThreads, (MagicInfo<T>::paired && !PHILOX) ? 3 : 2)
 pack_single_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T* __restrict__ mx,
                    int8_t* __restrict__ packed, ST* __restrict__ scale, ST* __restrict__ mn_out,
                    ST* __restrict__ mx_out, int64_t N, int64_t G, const T* __restrict__ noise,
@@ -213,7 +216,11 @@ pack_single_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T
         const bool ok = FULL || (n0 + s < N && gi < cnt);
         Oct<T> nz;
         const int64_t q = (n0 + s) * G + g0 + gi;
-        if (!stochastic || !ok) nz = zero_oct<T>();
+        if constexpr (PHILOX) {
+          static_assert(!PHILOX || FULL, "the generator-only variant covers whole tasks");
+          if (gi % NoiseShape<T>::GPC == 0) noise_block<T>(gen.key, (uint64_t)q, lane, nzb);
+          nz = nzb[gi % NoiseShape<T>::GPC];
+        } else if (!stochastic || !ok) nz = zero_oct<T>();
         else if (noise) nz = load_oct<T>(noise + q * kGroup + lane * kOct);
         else if (!FULL) nz = gen.get((uint64_t)q);
         else {                                          // FULL: q - gi is a multiple of the groups per call
@@ -369,6 +376,11 @@ int launch_pack(int bits, const void* data, const void* mn, const void* mx, int8
       kernel<<<grid, kThreads, smem, s>>>((const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, \
                                           (ST*)mn_out, (ST*)mx_out, N, G, (const T*)noise, stochastic, key, tb, \
                                           gave_up);                                                 \
+    } else if (full && stochastic && !noise) {                                                      \
+      auto kernel = pack_single_kernel<T, ST, BITS, FUSED, true, false, true>;                      \
+      kernel<<<persistent_grid(kernel, kThreads, tasks), kThreads, 0, s>>>(                         \
+          (const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, (ST*)mn_out, (ST*)mx_out, N, G, \
+          (const T*)noise, stochastic, key, tb, gave_up);                                           \
     } else if (full) {                                                                              \
       auto kernel = pack_single_kernel<T, ST, BITS, FUSED, true, false>;                            \
       kernel<<<persistent_grid(kernel, kThreads, tasks), kThreads, 0, s>>>(                         \
