@@ -125,6 +125,78 @@ enum class Op { kReluFwd, kMaskBwd, kDropoutFwd };
 //   kReluFwd:    y = x > 0 ? x : 0,           mask <- (x > 0)
 //   kDropoutFwd: y = keep ? x * inv : 0,      mask <- keep = (u > p)
 //   kMaskBwd:    grad_in = mask ? grad_out * inv : 0      (inv = 1 for ReLU)
+// One block of 1024 elements of a warp.  FULL: the block lies wholly inside the tensor, so
+// there is no per-row edge handling and the four loads (and stores) sit in one basic block.
+template <typename T, Op OP, bool FULL>
+ACTNN_DEV void mask_block(const T* __restrict__ in, T* __restrict__ out, int32_t* __restrict__ mask,
+                          int64_t numel, int64_t mask_words, int64_t blk, int lane, float inv, float p,
+                          const float* __restrict__ u, const NoiseKey& key) {
+  const int64_t e0 = blk * kBlockElems + lane * kOct;
+  Oct<T> x[kRows];
+  int valid[kRows];
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) {
+    const int64_t e = e0 + (int64_t)i * kGroup;
+    if constexpr (FULL) {
+      valid[i] = kOct;
+      x[i] = load_oct<T>(in + e);
+    } else {
+      valid[i] = (int)max((int64_t)0, min((int64_t)kOct, numel - e));
+      if (valid[i] == kOct) x[i] = load_oct<T>(in + e);
+      else if (valid[i] > 0) x[i] = load_partial<T>(in + e, valid[i]);
+      else x[i] = zero_oct<T>();
+    }
+  }
+  uint32_t keep = 0;                                 // byte i = keep-bits of row i
+  if constexpr (OP == Op::kMaskBwd) {
+    const int64_t w = blk * (kBlockElems / 32) + lane;
+    keep = words_to_bytes((FULL || w < mask_words) ? (uint32_t)__ldg(mask + w) : 0u, lane);
+  } else if constexpr (OP == Op::kReluFwd) {
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) keep |= positive_bits<T>(x[i]) << (8 * i);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      const int64_t oct = (e0 + (int64_t)i * kGroup) >> 3;
+      uint32_t kb = 0;
+      if (u) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) kb |= (j < valid[i] && __ldg(u + oct * 8 + j) > p ? 1u : 0u) << j;
+      } else {
+        const Philox4 r = noise_call(key, (uint64_t)oct);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t k = (r.v[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+          kb |= ((float)(k + 1u) * (1.0f / 65536.0f) > p ? 1u : 0u) << j;
+        }
+      }
+      keep |= kb << (8 * i);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) {
+    if (!FULL && valid[i] == 0) continue;
+    Oct<T> y = select_kept<T>(x[i], (keep >> (8 * i)) & 0xffu);
+    if constexpr (OP != Op::kReluFwd) { if (inv != 1.f) y = scale_oct<T>(y, inv); }
+    const int64_t e = e0 + (int64_t)i * kGroup;
+    if (FULL || valid[i] == kOct) store_oct<T>(out + e, y);
+    else store_partial<T>(out + e, y, valid[i]);
+  }
+  if constexpr (OP != Op::kMaskBwd) {
+    // bits past numel are already zero: rows / elements beyond the end contribute 0
+    uint32_t clipped = keep;
+    if constexpr (!FULL) {
+      clipped = 0;
+#pragma unroll
+      for (int i = 0; i < kRows; ++i)
+        clipped |= (((keep >> (8 * i)) & 0xffu) & ((1u << valid[i]) - 1u)) << (8 * i);
+    }
+    const uint32_t word = bytes_to_words(clipped, lane);
+    const int64_t w = blk * (kBlockElems / 32) + lane;
+    if (FULL || w < mask_words) mask[w] = (int32_t)word;
+  }
+}
+
 template <typename T, Op OP>
 __global__ void __launch_bounds__(kThreads)
 mask_kernel(const T* __restrict__ in, T* __restrict__ out, int32_t* __restrict__ mask, int64_t numel,
@@ -133,65 +205,11 @@ mask_kernel(const T* __restrict__ in, T* __restrict__ out, int32_t* __restrict__
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const int64_t blocks = (numel + kBlockElems - 1) / kBlockElems;
+  const int64_t whole = numel / kBlockElems;            // blocks that lie wholly inside the tensor
   const int64_t mask_words = (numel + 31) / 32;
-
   for (int64_t blk = warp; blk < blocks; blk += nwarps) {
-    const int64_t e0 = blk * kBlockElems + lane * kOct;
-    Oct<T> x[kRows];
-    int valid[kRows];
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-      const int64_t e = e0 + (int64_t)i * kGroup;
-      valid[i] = (int)max((int64_t)0, min((int64_t)kOct, numel - e));
-      if (valid[i] == kOct) x[i] = load_oct<T>(in + e);
-      else if (valid[i] > 0) x[i] = load_partial<T>(in + e, valid[i]);
-      else x[i] = zero_oct<T>();
-    }
-    uint32_t keep = 0;                                 // byte i = keep-bits of row i
-    if constexpr (OP == Op::kMaskBwd) {
-      const int64_t w = blk * (kBlockElems / 32) + lane;
-      keep = words_to_bytes(w < mask_words ? (uint32_t)__ldg(mask + w) : 0u, lane);
-    } else if constexpr (OP == Op::kReluFwd) {
-#pragma unroll
-      for (int i = 0; i < kRows; ++i) keep |= positive_bits<T>(x[i]) << (8 * i);
-    } else {
-#pragma unroll
-      for (int i = 0; i < kRows; ++i) {
-        const int64_t oct = (e0 + (int64_t)i * kGroup) >> 3;
-        uint32_t kb = 0;
-        if (u) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) kb |= (j < valid[i] && __ldg(u + oct * 8 + j) > p ? 1u : 0u) << j;
-        } else {
-          const Philox4 r = noise_call(key, (uint64_t)oct);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t k = (r.v[j >> 1] >> (16 * (j & 1))) & 0xffffu;
-            kb |= ((float)(k + 1u) * (1.0f / 65536.0f) > p ? 1u : 0u) << j;
-          }
-        }
-        keep |= kb << (8 * i);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-      if (valid[i] == 0) continue;
-      Oct<T> y = select_kept<T>(x[i], (keep >> (8 * i)) & 0xffu);
-      if constexpr (OP != Op::kReluFwd) { if (inv != 1.f) y = scale_oct<T>(y, inv); }
-      const int64_t e = e0 + (int64_t)i * kGroup;
-      if (valid[i] == kOct) store_oct<T>(out + e, y);
-      else store_partial<T>(out + e, y, valid[i]);
-    }
-    if constexpr (OP != Op::kMaskBwd) {
-      // bits past numel are already zero: rows / elements beyond the end contribute 0
-      uint32_t clipped = 0;
-#pragma unroll
-      for (int i = 0; i < kRows; ++i)
-        clipped |= (((keep >> (8 * i)) & 0xffu) & ((1u << valid[i]) - 1u)) << (8 * i);
-      const uint32_t word = bytes_to_words(clipped, lane);
-      const int64_t w = blk * (kBlockElems / 32) + lane;
-      if (w < mask_words) mask[w] = (int32_t)word;
-    }
+    if (blk < whole) mask_block<T, OP, true>(in, out, mask, numel, mask_words, blk, lane, inv, p, u, key);
+    else mask_block<T, OP, false>(in, out, mask, numel, mask_words, blk, lane, inv, p, u, key);
   }
 }
 

@@ -7,38 +7,48 @@ namespace actnn {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kBundle = 4;
 
 // ---------------------------------------------------------------------------- minimax
-// cols == 256: a warp takes four consecutive rows (four independent vector loads per
-// lane), reduces each with one redux.sync.min/max.f32, and lanes 0..3 write the results.
+// cols == 256: a warp takes kMinimaxRows consecutive rows (as many independent vector loads
+// per lane), reduces each with one redux.sync.min/max.f32, and the first lanes write the
+// results.  FULL tasks (all rows present) carry no per-row predicate, so the loads sit in one
+// basic block and are issued back to back.
+constexpr int kMinimaxRows = 8;
+
+template <typename T, bool FULL>
+ACTNN_DEV void minimax256_task(const T* __restrict__ data, T* __restrict__ mn, T* __restrict__ mx, int64_t rows,
+                               int64_t r0, int lane) {
+  const int cnt = FULL ? kMinimaxRows : (int)min((int64_t)kMinimaxRows, rows - r0);
+  Oct<T> x[kMinimaxRows];
+#pragma unroll
+  for (int i = 0; i < kMinimaxRows; ++i)
+    x[i] = (FULL || i < cnt) ? load_oct<T>(data + (r0 + i) * kGroup + lane * kOct) : zero_oct<T>();
+  float my_mn = 0.f, my_mx = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMinimaxRows; ++i) {
+    float lo, hi;
+    oct_minmax<T>(x[i], lo, hi);
+    lo = warp_min(lo);
+    hi = warp_max(hi);
+    if (lane == i) { my_mn = lo; my_mx = hi; }
+  }
+  if (lane < cnt) {
+    store_scalar<T>(mn, r0 + lane, my_mn);
+    store_scalar<T>(mx, r0 + lane, my_mx);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 minimax256_kernel(const T* __restrict__ data, T* __restrict__ mn, T* __restrict__ mx, int64_t rows) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
-  const int64_t total = (rows + kBundle - 1) / kBundle;
+  const int64_t total = (rows + kMinimaxRows - 1) / kMinimaxRows;
+  const int64_t whole = rows / kMinimaxRows;
   for (int64_t task = warp; task < total; task += nwarps) {
-    const int64_t r0 = task * kBundle;
-    const int cnt = (int)min((int64_t)kBundle, rows - r0);
-    Oct<T> x[kBundle];
-#pragma unroll
-    for (int i = 0; i < kBundle; ++i)
-      x[i] = i < cnt ? load_oct<T>(data + (r0 + i) * kGroup + lane * kOct) : zero_oct<T>();
-    float my_mn = 0.f, my_mx = 0.f;
-#pragma unroll
-    for (int i = 0; i < kBundle; ++i) {
-      float lo, hi;
-      oct_minmax<T>(x[i], lo, hi);
-      lo = warp_min(lo);
-      hi = warp_max(hi);
-      if (lane == i) { my_mn = lo; my_mx = hi; }
-    }
-    if (lane < cnt) {
-      store_scalar<T>(mn, r0 + lane, my_mn);
-      store_scalar<T>(mx, r0 + lane, my_mx);
-    }
+    if (task < whole) minimax256_task<T, true>(data, mn, mx, rows, task * kMinimaxRows, lane);
+    else minimax256_task<T, false>(data, mn, mx, rows, task * kMinimaxRows, lane);
   }
 }
 
@@ -70,7 +80,7 @@ template <typename T>
 int launch_minimax(const void* data, void* mn, void* mx, int64_t rows, int64_t cols, cudaStream_t s) {
   const int64_t cap = (int64_t)device_info().sm_count * 8;
   if (cols == kGroup) {
-    const int64_t tasks = (rows + kBundle - 1) / kBundle;
+    const int64_t tasks = (rows + kMinimaxRows - 1) / kMinimaxRows;
     const int grid = (int)max((int64_t)1, min((tasks + 7) / 8, cap));
     minimax256_kernel<T><<<grid, kThreads, 0, s>>>((const T*)data, (T*)mn, (T*)mx, rows);
   } else {
