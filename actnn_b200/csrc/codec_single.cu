@@ -370,7 +370,13 @@ int launch_pack(int bits, const void* data, const void* mn, const void* mx, int8
     constexpr int smem = (kThreads / 32) * (kStages * Sh::OCTS * kGroup * (int)sizeof(T) + kStages * 8); \
     const int64_t tasks = ((N + Sh::WPT - 1) / Sh::WPT) * ((G + Sh::GP - 1) / Sh::GP);              \
     const bool full = N % Sh::WPT == 0 && G % Sh::GP == 0;                                          \
-    if (full && can_stage) {                                                                        \
+    if (full && can_stage && stochastic && !noise) {                                                \
+      auto kernel = pack_single_kernel<T, ST, BITS, FUSED, true, true, true>;                       \
+      const int grid = persistent_grid(kernel, kThreads, tasks, smem);                              \
+      kernel<<<grid, kThreads, smem, s>>>((const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, \
+                                          (ST*)mn_out, (ST*)mx_out, N, G, (const T*)noise, stochastic, key, tb, \
+                                          gave_up);                                                 \
+    } else if (full && can_stage) {                                                                 \
       auto kernel = pack_single_kernel<T, ST, BITS, FUSED, true, true>;                             \
       const int grid = persistent_grid(kernel, kThreads, tasks, smem);                              \
       kernel<<<grid, kThreads, smem, s>>>((const T*)data, (const T*)mn, (const T*)mx, packed, (ST*)scale, \
