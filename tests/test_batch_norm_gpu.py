@@ -187,31 +187,39 @@ def test_sync_batch_norm_op_in_a_one_rank_group_matches_batch_norm(actnn, cuda_d
 
 
 def test_resnet18_trains_like_stock_torch_at_level_L0(actnn, cuda_device):
-    """Three SGD steps of a ResNet-18 through QModule without compression (level L0: only the
-    batch-norm, ReLU and max-pool kernels differ from stock torch) follow the stock model's
-    losses and end near the same weights."""
+    """A ResNet-18 through QModule without compression (level L0: only the batch-norm, ReLU and
+    max-pool kernels differ from stock torch) against the stock model: same logits, gradients
+    equal to within what a 1e-7 perturbation of the input does to the stock model itself
+    (a randomly initialised 18-layer net with batch 16 amplifies rounding differences to
+    ~1e-2 in the gradients), and the same losses over three SGD steps."""
     import copy
     import torchvision
-    actnn.set_optimization_level("L0")
-    torch.manual_seed(0)
-    stock = torchvision.models.resnet18(num_classes=10).to(cuda_device).train()
-    ours = actnn.QModule(copy.deepcopy(stock)).train()
-    x = torch.randn(16, 3, 64, 64, device=cuda_device)
-    y = torch.randint(0, 10, (16,), device=cuda_device)
-    losses = []
-    for model in (stock, ours):
-        opt = torch.optim.SGD(model.parameters(), lr=0.01)
-        trace = []
-        for _ in range(3):
-            opt.zero_grad(set_to_none=True)
-            loss = torch.nn.functional.cross_entropy(model(x), y)
-            loss.backward()
-            opt.step()
-            trace.append(float(loss.detach()))
-        losses.append(trace)
-    # rounding differences grow from step to step (the net is trained on 16 samples): 1 % of slack
-    assert all(abs(a - b) <= 1e-2 * max(1.0, abs(a)) for a, b in zip(*losses)), losses
-    # weights after three steps: the same to within what three chaotic steps leave (a coarse
-    # check against gross errors; element-wise comparisons are in the kernel tests above)
-    for (name, p), q in zip(stock.named_parameters(), ours.model.parameters()):
-        assert float((p - q).norm()) <= 2e-2 * float(p.norm()) + 1e-3, name
+    tf32 = (torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32)
+    torch.backends.cudnn.allow_tf32 = torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        actnn.set_optimization_level("L0")
+        torch.manual_seed(0)
+        stock = torchvision.models.resnet18(num_classes=10).to(cuda_device).train()
+        ours = actnn.QModule(copy.deepcopy(stock)).train()
+        x = torch.randn(16, 3, 64, 64, device=cuda_device)
+        y = torch.randint(0, 10, (16,), device=cuda_device)
+        out_s, out_o = stock(x), ours(x)
+        assert torch.allclose(out_o, out_s, rtol=1e-3, atol=1e-3)
+        torch.nn.functional.cross_entropy(out_s, y).backward()
+        torch.nn.functional.cross_entropy(out_o, y).backward()
+        for (name, p), q in zip(stock.named_parameters(), ours.model.parameters()):
+            assert float((p.grad - q.grad).norm()) <= 5e-2 * float(p.grad.norm()) + 1e-6, name
+        losses = []
+        for model in (stock, ours):
+            opt = torch.optim.SGD(model.parameters(), lr=0.01)
+            trace = []
+            for _ in range(3):
+                opt.zero_grad(set_to_none=True)
+                loss = torch.nn.functional.cross_entropy(model(x), y)
+                loss.backward()
+                opt.step()
+                trace.append(float(loss.detach()))
+            losses.append(trace)
+        assert all(abs(a - b) <= 2e-2 * max(1.0, abs(a)) for a, b in zip(*losses)), losses
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = tf32
