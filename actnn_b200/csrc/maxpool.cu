@@ -162,7 +162,11 @@ max_pool_backward_kernel(const T* __restrict__ gy, const int8_t* __restrict__ id
 // window selected if that lies in its segment.  Index arithmetic is paid once per eight
 // outputs, the store is one 16-byte vector when the row allows it, and every position
 // receives its terms in the general kernel's order (window rows, then columns, ascending).
-template <typename T, int NWIN>
+// FIXED_SW / FIXED_KW / FIXED_D0 > -100: the column stride, the window width and the offset
+// `wo_lo * SW - PW - w0` of the first candidate column against the segment are compile-time
+// (they do not depend on the segment when 8 % SW == 0); a window then reaches only FIXED_KW
+// known positions of the segment instead of being compared against all eight.
+template <typename T, int NWIN, int FIXED_SW = 0, int FIXED_KW = 0, int FIXED_D0 = -100>
 __global__ void __launch_bounds__(256)
 max_pool_backward_row_kernel(const T* __restrict__ gy, const int8_t* __restrict__ idx, T* __restrict__ gx,
                              uint32_t total_segments, int segs_per_row, PoolGeom g, uint64_t kh_of, uint64_t kw_of,
@@ -208,9 +212,18 @@ max_pool_backward_row_kernel(const T* __restrict__ gy, const int8_t* __restrict_
         const int c = code[a][b] & 15;
         const int kh = (int)((kh_of >> (4 * c)) & 15), kw = (int)((kw_of >> (4 * c)) & 15);
         const bool live = ho <= ho_hi && wo <= wo_hi && kh == kh_need;
-        const int target = live ? wo * g.SW - g.PW + kw - w0 : -1;   // position inside the segment
+        if constexpr (FIXED_D0 > -100) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += target == j ? grad[a][b] : 0.f;
+          for (int t = 0; t < FIXED_KW; ++t) {
+            constexpr int kFirst = FIXED_D0;
+            const int j = kFirst + FIXED_SW * b + t;             // compile-time after unrolling
+            if (j >= 0 && j < 8) acc[j] += (live && kw == t) ? grad[a][b] : 0.f;
+          }
+        } else {
+          const int target = live ? wo * g.SW - g.PW + kw - w0 : -1;   // position inside the segment
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += target == j ? grad[a][b] : 0.f;
+        }
       }
     }
     T* out = gx + (int64_t)nc * plane_elems + h * g.W + w0;
@@ -258,7 +271,11 @@ int launch_backward(const void* gy, const int8_t* idx, void* gx, int64_t planes,
     const int vec = g.W % 8 == 0 && aligned(gx, 16);
     const int64_t blocks = (total_segments + 255) / 256;
     const int grid = (int)max((int64_t)1, min(blocks, (int64_t)device_info().sm_count * 16));
-    if (nwin <= 6)
+    if (g.KW == 3 && g.SW == 2 && g.PW == 1)                     // the stem pooling of the ResNets: offset -1 always
+      max_pool_backward_row_kernel<T, 5, 2, 3, -1><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx,
+                                                                        (uint32_t)total_segments, segs, g, kh_of,
+                                                                        kw_of, vec);
+    else if (nwin <= 6)
       max_pool_backward_row_kernel<T, 6><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, (uint32_t)total_segments,
                                                               segs, g, kh_of, kw_of, vec);
     else
