@@ -25,7 +25,7 @@ from torch.nn.modules.utils import _pair, _single, _triple
 
 from .conf import config
 from .cpp_extension import backward_func as ext_backward_func
-from .cpp_extension import minimax as ext_minimax
+from .cpp_extension import minimax as ext_minimax  # noqa: F401  (kept under the name the reference imports)
 from .cpp_extension import quantization as ext_quantization
 from .qscheme import group_minimax, to_groups
 from .utils import compute_tensor_bytes, empty_cache, get_memory_usage, swap_to_cpu, swap_to_gpu

@@ -22,7 +22,7 @@ from __future__ import annotations
 
 import threading
 import weakref
-from typing import Callable, Dict, List, Optional
+from typing import Callable, Dict, List
 
 import torch
 
