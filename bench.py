@@ -332,6 +332,19 @@ def run_ours(args):
             pm[(r + 4) % POOL].data_ptr(), bt.data_ptr(), offs.data_ptr(), scales[(r + 4) % POOL].data_ptr(),
             mnx[(r + 4) % POOL][0].data_ptr(), outs[r % 2].data_ptr(), N, G, gs, F16, F16, stream))
         kernels["unpack_mixed_2b_avg"] = {"ms": round(ms, 5), "gbs": round(one_way / ms / 1e6, 1)}
+        # the whole adaptive compress in one call: min/max, sensitivities, greedy, pack (X is read twice)
+        ws_bytes = lib.actnn_compress_mixed_workspace(N, G, F16)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        c_out = torch.empty(N, dtype=torch.float32, device=dev)
+        bt2, offs2 = torch.empty_like(bt), torch.empty_like(offs)
+        mn_o = torch.empty(N * G, dtype=dt, device=dev)
+        ms = time_kernel(lambda r: lib.actnn_compress_mixed(
+            xs[r % POOL].data_ptr(), pm[r % POOL].data_ptr(), scales[r % POOL].data_ptr(), mn_o.data_ptr(),
+            bt2.data_ptr(), offs2.data_ptr(), c_out.data_ptr(), ws.data_ptr(), ws_bytes, N, G, gs, F16, F16,
+            gs / float(H * W), 1.0, None, 8, float(2 * N), 1, None, 7, 4 * r, stream))
+        kernels["compress_mixed_2b_avg_one_call"] = {
+            "ms": round(ms, 5), "gbs": round((one_way + elements * 2.0) / ms / 1e6, 1),
+            "note": "minimax + sensitivity + greedy + pack; algorithmic bytes count the two reads of X"}
         ms = time_kernel(lambda r: lib.actnn_calc_precision(Cs.data_ptr(), None, N, 8, float(2 * N), bt.data_ptr(),
                                                            offs.data_ptr(), G, gs, None, 0, stream))
         kernels["calc_precision_n256"] = {"ms": round(ms, 5)}
