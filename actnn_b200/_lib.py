@@ -113,15 +113,22 @@ def stream_of(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+_fns = {}
+
+
 def call(name: str, tensor_for_device: torch.Tensor, *args) -> None:
     """Invoke ``name`` with the tensor's device current and check the status."""
-    lib = load()
-    dev = tensor_for_device.device
-    if dev.index is not None and dev.index != torch.cuda.current_device():
-        with torch.cuda.device(dev):
-            check(getattr(lib, name)(*args), name)
+    fn = _fns.get(name)
+    if fn is None:
+        fn = _fns[name] = getattr(load(), name)
+    idx = tensor_for_device.device.index
+    if idx is not None and idx != torch.cuda.current_device():
+        with torch.cuda.device(idx):
+            status = fn(*args)
     else:
-        check(getattr(lib, name)(*args), name)
+        status = fn(*args)
+    if status:
+        check(status, name)
 
 
 def next_philox(device: torch.device):
