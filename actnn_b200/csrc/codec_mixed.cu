@@ -153,6 +153,167 @@ pack_mixed_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T*
   }
 }
 
+// ---------------------------------------------------------------------------- pack, flat tasks
+// Fast path for G % 4 == 0 and G >= 32 (every layer of the usual networks).  A warp task is
+// 32 consecutive groups of the flattened [N * G] list:
+//   * lane l prepares group q0 + l: its sample, width and stream position, one coalesced load
+//     of min / max, ONE division, coalesced stores of scale / min.  All 32 lanes work, so the
+//     per-group cost is a quarter of what a four-group bundle with four active lanes pays;
+//   * the task is then worked off as eight bundles of four groups (one generator call per
+//     lane, `B` transposes, `B` coalesced 128-byte stores).  A bundle never straddles two
+//     samples because G % 4 == 0, so its width is warp-uniform;
+//   * the octets of the next bundle (also across the task boundary) are requested before the
+//     current one is quantized: a warp always has loads in flight.
+constexpr int kFlatGroups = 32;       // groups per task
+constexpr int kFlatBundle = 4;        // groups per bundle
+enum NoiseMode { kNoisePhilox = 0, kNoiseTensor = 1, kNoiseNone = 2 };
+
+// Device counter of bundles whose width was outside 1..8 (nothing is written for them).
+__device__ unsigned g_bad_width_bundles;
+
+// (mn', scale) of the lane's own group in the form the quantizer consumes.
+template <typename T> struct LaneParams { uint32_t a, b; };
+template <typename T> ACTNN_DEV LaneParams<T> lane_params(const GroupParams& gp) {
+  LaneParams<T> p;
+  if constexpr (sizeof(T) == 4) {
+    p.a = __float_as_uint(gp.mn1);
+    p.b = __float_as_uint(gp.scale);
+  } else {
+    p.a = bits_of<T>(gp.mn1) * 0x00010001u;
+    p.b = bits_of<T>(gp.scale) * 0x00010001u;
+  }
+  return p;
+}
+template <typename T> ACTNN_DEV QP<T> fetch_lane_params(const LaneParams<T>& mine, int src_lane) {
+  const uint32_t a = __shfl_sync(kFull, mine.a, src_lane), b = __shfl_sync(kFull, mine.b, src_lane);
+  QP<T> q;
+  if constexpr (sizeof(T) == 4) {
+    q.mn1 = __uint_as_float(a);
+    q.scale = __uint_as_float(b);
+  } else {
+    q.mn2 = *reinterpret_cast<const decltype(q.mn2)*>(&a);
+    q.sc2 = *reinterpret_cast<const decltype(q.sc2)*>(&b);
+  }
+  return q;
+}
+
+template <typename T, int B, int MODE, bool CLAMP_LOW>
+ACTNN_DEV void pack_flat_bundle(const Oct<T> (&x)[kFlatBundle], const LaneParams<T>& mine, int first_lane,
+                                int64_t q, int32_t* __restrict__ out, const T* __restrict__ noise,
+                                const NoiseKey& key, const TransposePlan& plan, int lane) {
+  constexpr int GPC = NoiseShape<T>::GPC;
+  uint32_t S[B];
+#pragma unroll
+  for (int k = 0; k < B; ++k) S[k] = 0u;
+  Oct<T> nzb[GPC];
+#pragma unroll
+  for (int gi = 0; gi < kFlatBundle; ++gi) {
+    const QP<T> qp = fetch_lane_params<T>(mine, first_lane + gi);
+    Oct<T> nz;
+    if constexpr (MODE == kNoisePhilox) {
+      if (gi % GPC == 0) noise_block<T>(key, (uint64_t)(q + gi), lane, nzb);
+      nz = nzb[gi % GPC];
+    } else if constexpr (MODE == kNoiseTensor) {
+      nz = load_oct<T>(noise + (q + gi) * kGroup + lane * kOct);
+    } else {
+      nz = zero_oct<T>();
+    }
+    uint32_t lo, hi;
+    row_from_magic<T, B>(quantize_oct<T, CLAMP_LOW, B>(x[gi], nz, qp), lo, hi);
+    if (gi == 0) put_row<B, 0 * 8 * B>(S, lo, hi);
+    if (gi == 1) put_row<B, 1 * 8 * B>(S, lo, hi);
+    if (gi == 2) put_row<B, 2 * 8 * B>(S, lo, hi);
+    if (gi == 3) put_row<B, 3 * 8 * B>(S, lo, hi);
+  }
+#pragma unroll
+  for (int k = 0; k < B; ++k) out[k * 32 + lane] = (int32_t)warp_transpose32(S[k], plan);
+}
+
+template <typename T, typename ST, int MODE, bool CLAMP_LOW>
+__global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 2)
+pack_mixed_flat_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T* __restrict__ mx,
+                       const int32_t* __restrict__ bits, const int64_t* __restrict__ word_offsets,
+                       int32_t* __restrict__ packed, ST* __restrict__ scale, ST* __restrict__ mn_out,
+                       int64_t Q, int64_t G, const T* __restrict__ noise, const NoiseKey key) {
+  constexpr bool PREFETCH = sizeof(T) == 2;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
+  const TransposePlan plan = make_transpose_plan(lane);
+  const int64_t tasks = (Q + kFlatGroups - 1) / kFlatGroups;
+  if (warp >= tasks) return;
+
+  // (sample, group) of the task's first group, advanced without divisions inside the loop
+  int64_t q0 = warp * kFlatGroups;
+  int64_t n0 = q0 / G;
+  int64_t r0 = q0 - n0 * G;
+  const int64_t stride = nwarps * kFlatGroups;
+  const int64_t step_n = stride / G, step_r = stride - step_n * G;
+
+  auto load_bundle = [&](Oct<T> (&dst)[kFlatBundle], int64_t q) {
+#pragma unroll
+    for (int gi = 0; gi < kFlatBundle; ++gi) dst[gi] = load_oct<T>(data + (q + gi) * kGroup + lane * kOct);
+  };
+
+  // Two register buffers used alternately (even bundles read A and fill B, odd ones the
+  // reverse), so the prefetched octets never have to be moved.
+  Oct<T> bufA[kFlatBundle], bufB[PREFETCH ? kFlatBundle : 1];
+  if constexpr (PREFETCH) load_bundle(bufA, q0);
+  for (; q0 < Q; q0 += stride) {
+    // ---- this lane's group
+    const int64_t q = q0 + lane;
+    int64_t n = n0, r = r0 + lane;
+    if (r >= G) { r -= G; ++n; }                              // G >= 32: at most one wrap
+    int b_l = 0;
+    int64_t off_l = 0;
+    LaneParams<T> mine = {0u, 0u};
+    if (q < Q) {
+      b_l = __ldg(bits + n);
+      off_l = __ldg(word_offsets + n) + r * (8 * b_l);
+      const float gmn = load_scalar<T>(mn, q), gmx = load_scalar<T>(mx, q);
+      const GroupParams gp = prepare_group<T>(gmn, gmx, b_l);
+      store_scalar<ST>(scale, q, gp.scale);
+      if (mn_out) store_scalar<ST>(mn_out, q, gmn);
+      mine = lane_params<T>(gp);
+    }
+    const int64_t q0_next = q0 + stride;
+    auto bundle = [&](Oct<T> (&cur)[kFlatBundle], Oct<T> (&nxt)[PREFETCH ? kFlatBundle : 1], int k) {
+      const int64_t qk = q0 + k * kFlatBundle;
+      if constexpr (PREFETCH) {
+        const int64_t qn = (k + 1 < kFlatGroups / kFlatBundle) ? qk + kFlatBundle : q0_next;
+        if (qn < Q) load_bundle(nxt, qn);
+      } else {
+        load_bundle(cur, qk);
+      }
+      const int first = k * kFlatBundle;
+      const int b = __shfl_sync(kFull, b_l, first);
+      const uint32_t olo = __shfl_sync(kFull, (uint32_t)off_l, first);
+      const uint32_t ohi = __shfl_sync(kFull, (uint32_t)((uint64_t)off_l >> 32), first);
+      int32_t* out = packed + (int64_t)(((uint64_t)ohi << 32) | olo);
+#define ACTNN_CASE(B)                                                                                  \
+      case B: pack_flat_bundle<T, B, MODE, CLAMP_LOW>(cur, mine, first, qk, out, noise, key, plan, lane); break;
+      switch (b) {
+        ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
+        ACTNN_CASE(8)
+        default:
+          if (lane == 0) atomicAdd(&g_bad_width_bundles, 1u);
+          break;
+      }
+#undef ACTNN_CASE
+    };
+    for (int k = 0; k < kFlatGroups / kFlatBundle; k += 2) {
+      if (q0 + k * kFlatBundle >= Q) break;                   // warp-uniform
+      bundle(bufA, bufB, k);
+      if (q0 + (k + 1) * kFlatBundle >= Q) break;
+      if constexpr (PREFETCH) bundle(bufB, bufA, k + 1);
+      else bundle(bufA, bufB, k + 1);
+    }
+    n0 += step_n;
+    r0 += step_r;
+    if (r0 >= G) { r0 -= G; ++n0; }
+  }
+}
+
 // ---------------------------------------------------------------------------- unpack
 // Decoding a group needs only 2^B distinct outputs, code / scale + min for code = 0..2^B-1.
 // Lanes compute those once (one IEEE division per lane for up to four groups at a time)
@@ -295,6 +456,158 @@ unpack_mixed_kernel(const int32_t* __restrict__ packed, const int32_t* __restric
   }
 }
 
+// ---------------------------------------------------------------------------- unpack, flat tasks
+// Same task shape as the flat pack: lane l owns group q0 + l of a task of 32 groups (its
+// sample, width, stream position, scale and min come from coalesced loads), and eight bundles
+// of four groups are decoded with the words of the next bundle already requested.  For 16-bit
+// outputs at 1 or 2 bits the lane also computes the 2^B decoded values of its own group once
+// per task (packed in two registers); a bundle then fetches them with two shuffles per group.
+template <typename T, int B>
+ACTNN_DEV void unpack_flat_bundle(const uint32_t (&words)[8], float sc_l, float m_l, uint32_t t01_l, uint32_t t23_l,
+                                  int first, int64_t q, T* __restrict__ out, const TransposePlan& plan, int lane) {
+  constexpr int E = 1 << (B < 6 ? B : 5);              // table entries per group
+  constexpr int GPC = (32 / E) < kFlatBundle ? (32 / E) : kFlatBundle;   // groups served by one table
+  constexpr bool PAIRS = sizeof(T) == 2 && B <= 2;
+  uint32_t S[B];
+#pragma unroll
+  for (int k = 0; k < B; ++k) S[k] = warp_transpose32(words[k], plan);
+  uint32_t entry = 0u;
+#pragma unroll
+  for (int gi = 0; gi < kFlatBundle; ++gi) {
+    if constexpr (!PAIRS && B < 6) {
+      if (gi % GPC == 0) {                               // (re)build the table for groups gi .. gi+GPC-1
+        const int g = first + ((gi + lane / E) & (kFlatBundle - 1));
+        const float sc = __shfl_sync(kFull, sc_l, g), m = __shfl_sync(kFull, m_l, g);
+        entry = dequant_bits<T>((float)(lane % E), sc, m);
+      }
+    }
+    uint32_t lo = 0u, hi = 0u;                           // this group's row
+    if (gi == 0) { lo = get_bits<0 * 8 * B, (8 * B < 32 ? 8 * B : 32)>(S); if constexpr (8 * B > 32) hi = get_bits<0 * 8 * B + 32, 8 * B - 32>(S); }
+    if (gi == 1) { lo = get_bits<1 * 8 * B, (8 * B < 32 ? 8 * B : 32)>(S); if constexpr (8 * B > 32) hi = get_bits<1 * 8 * B + 32, 8 * B - 32>(S); }
+    if (gi == 2) { lo = get_bits<2 * 8 * B, (8 * B < 32 ? 8 * B : 32)>(S); if constexpr (8 * B > 32) hi = get_bits<2 * 8 * B + 32, 8 * B - 32>(S); }
+    if (gi == 3) { lo = get_bits<3 * 8 * B, (8 * B < 32 ? 8 * B : 32)>(S); if constexpr (8 * B > 32) hi = get_bits<3 * 8 * B + 32, 8 * B - 32>(S); }
+    Oct<T> o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+    if constexpr (PAIRS) {
+      const uint32_t t01 = __shfl_sync(kFull, t01_l, first + gi);
+      const uint32_t t23 = B == 2 ? __shfl_sync(kFull, t23_l, first + gi) : t01;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                      // four elements per step
+        const uint32_t y = spread_codes_to_bytes<B>((lo >> (4 * B * h)) & ((1u << (4 * B)) - 1u));
+        const uint32_t sel = y * 0x22u + 0x10101010u;    // byte pair (2c, 2c+1) per element
+        ow[2 * h] = __byte_perm(t01, t23, sel);
+        ow[2 * h + 1] = __byte_perm(t01, t23, sel >> 16);
+      }
+    } else {
+      uint32_t v[8];
+      const uint32_t S2[2] = {lo, hi};
+      uint32_t code[8];
+      get_codes<B, 0>(S2, code);
+      if constexpr (B < 6) {
+        const int base = (gi % GPC) * E;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __shfl_sync(kFull, entry, base + (int)code[j]);
+      } else {
+        const float sc = __shfl_sync(kFull, sc_l, first + gi), m = __shfl_sync(kFull, m_l, first + gi);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = dequant_bits<T>((float)code[j], sc, m);
+      }
+      if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ow[j] = v[j];
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) ow[k] = v[2 * k] | (v[2 * k + 1] << 16);
+      }
+    }
+    store_oct<T>(out + (q + gi) * kGroup + lane * kOct, o);
+  }
+}
+
+template <typename T, typename ST>
+__global__ void __launch_bounds__(kThreads, 3)
+unpack_mixed_flat_kernel(const int32_t* __restrict__ packed, const int32_t* __restrict__ bits,
+                         const int64_t* __restrict__ word_offsets, const ST* __restrict__ scale,
+                         const ST* __restrict__ mn, T* __restrict__ out, int64_t Q, int64_t G) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
+  const TransposePlan plan = make_transpose_plan(lane);
+  const int64_t tasks = (Q + kFlatGroups - 1) / kFlatGroups;
+  if (warp >= tasks) return;
+  int64_t q0 = warp * kFlatGroups;
+  int64_t n0 = q0 / G;
+  int64_t r0 = q0 - n0 * G;
+  const int64_t stride = nwarps * kFlatGroups;
+  const int64_t step_n = stride / G, step_r = stride - step_n * G;
+
+  for (; q0 < Q; q0 += stride) {
+    const int64_t q = q0 + lane;
+    int64_t n = n0, r = r0 + lane;
+    if (r >= G) { r -= G; ++n; }
+    int b_l = 0;
+    int64_t off_l = 0;
+    float sc_l = 1.f, m_l = 0.f;
+    uint32_t t01_l = 0u, t23_l = 0u;
+    if (q < Q) {
+      b_l = __ldg(bits + n);
+      off_l = __ldg(word_offsets + n) + r * (8 * b_l);
+      sc_l = load_scalar<ST>(scale, q);
+      m_l = load_scalar<ST>(mn, q);
+      if constexpr (sizeof(T) == 2) {
+        if (b_l <= 2) {
+          const uint32_t e0 = dequant_bits<T>(0.f, sc_l, m_l), e1 = dequant_bits<T>(1.f, sc_l, m_l);
+          t01_l = e0 | (e1 << 16);
+          if (b_l == 2) {
+            const uint32_t e2 = dequant_bits<T>(2.f, sc_l, m_l), e3 = dequant_bits<T>(3.f, sc_l, m_l);
+            t23_l = e2 | (e3 << 16);
+          }
+        }
+      }
+    }
+    // words of bundle k: word kk * 32 + lane of its 32 * b words, kk < b
+    auto request = [&](uint32_t (&w)[8], int k, int& b_out, int64_t& qk_out) {
+      const int first = k * kFlatBundle;
+      qk_out = q0 + first;
+      b_out = __shfl_sync(kFull, b_l, first);
+      const uint32_t olo = __shfl_sync(kFull, (uint32_t)off_l, first);
+      const uint32_t ohi = __shfl_sync(kFull, (uint32_t)((uint64_t)off_l >> 32), first);
+      const int32_t* in = packed + (int64_t)(((uint64_t)ohi << 32) | olo) + lane;
+      if (qk_out < Q) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          if (kk < b_out) w[kk] = (uint32_t)__ldg(in + kk * 32);
+      }
+    };
+    uint32_t wA[8], wB[8];
+    int bA = 0, bB = 0;
+    int64_t qA = 0, qB = 0;
+    request(wA, 0, bA, qA);
+    auto decode = [&](const uint32_t (&w)[8], int b, int64_t qk, int k) {
+#define ACTNN_CASE(B) \
+      case B: unpack_flat_bundle<T, B>(w, sc_l, m_l, t01_l, t23_l, k * kFlatBundle, qk, out, plan, lane); break;
+      switch (b) {
+        ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
+        ACTNN_CASE(8)
+        default: break;                                    // the pack kernel counted and skipped it too
+      }
+#undef ACTNN_CASE
+    };
+    for (int k = 0; k < kFlatGroups / kFlatBundle; k += 2) {
+      if (qA >= Q) break;                                  // warp-uniform
+      request(wB, k + 1, bB, qB);
+      decode(wA, bA, qA, k);
+      if (qB >= Q) break;
+      if (k + 2 < kFlatGroups / kFlatBundle) request(wA, k + 2, bA, qA);
+      else qA = Q;
+      decode(wB, bB, qB, k + 1);
+    }
+    n0 += step_n;
+    r0 += step_r;
+    if (r0 >= G) { r0 -= G; ++n0; }
+  }
+}
+
 // ---------------------------------------------------------------------------- prefix
 // word_offsets[n] = (G * gs / 32) * sum_{m < n} bits[m]; one block, chunked scan.
 __global__ void __launch_bounds__(1024)
@@ -335,14 +648,39 @@ bits_prefix_kernel(const int32_t* __restrict__ bits, int64_t N, int64_t words_pe
   if (threadIdx.x == 0) word_offsets[N] = carry * words_per_bit;
 }
 
+template <typename T, typename ST, int MODE, bool CLAMP_LOW>
+void launch_pack_flat(const void* data, const void* mn, const void* mx, const int32_t* bits,
+                      const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out, int64_t N,
+                      int64_t G, const void* noise, const NoiseKey& key, cudaStream_t stream) {
+  auto kernel = pack_mixed_flat_kernel<T, ST, MODE, CLAMP_LOW>;
+  const int64_t tasks = (N * G + kFlatGroups - 1) / kFlatGroups;
+  kernel<<<persistent_grid(kernel, kThreads, tasks), kThreads, 0, stream>>>(
+      (const T*)data, (const T*)mn, (const T*)mx, bits, word_offsets, packed, (ST*)scale, (ST*)mn_out, N * G, G,
+      (const T*)noise, key);
+}
+
 template <typename T, typename ST>
 int launch_pack(const void* data, const void* mn, const void* mx, const int32_t* bits,
                 const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out, int64_t N,
                 int64_t G, int stochastic, const void* noise, uint64_t seed, uint64_t offset,
-                cudaStream_t stream) {
+                bool min_is_exact, cudaStream_t stream) {
   constexpr int GPB = PackShape<T>::GPB;
   const int64_t tasks = N * ((G + GPB - 1) / GPB);
   const NoiseKey key = make_noise_key(seed, offset);
+  if (G % kFlatBundle == 0 && G >= kFlatGroups) {
+#define ACTNN_FLAT(MODE)                                                                                     \
+    if (min_is_exact)                                                                                        \
+      launch_pack_flat<T, ST, MODE, false>(data, mn, mx, bits, word_offsets, packed, scale, mn_out, N, G, noise, \
+                                           key, stream);                                                     \
+    else                                                                                                     \
+      launch_pack_flat<T, ST, MODE, true>(data, mn, mx, bits, word_offsets, packed, scale, mn_out, N, G, noise, \
+                                          key, stream);
+    if (!stochastic) { ACTNN_FLAT(kNoiseNone) }
+    else if (noise) { ACTNN_FLAT(kNoiseTensor) }
+    else { ACTNN_FLAT(kNoisePhilox) }
+#undef ACTNN_FLAT
+    return check_launch();
+  }
   if (G % GPB == 0 && stochastic && !noise)
     pack_mixed_kernel<T, ST, true, true><<<persistent_grid(pack_mixed_kernel<T, ST, true, true>, kThreads, tasks),
                                            kThreads, 0, stream>>>(
@@ -364,6 +702,13 @@ int launch_pack(const void* data, const void* mn, const void* mx, const int32_t*
 template <typename T, typename ST>
 int launch_unpack(const int32_t* packed, const int32_t* bits, const int64_t* word_offsets,
                   const void* scale, const void* mn, void* out, int64_t N, int64_t G, cudaStream_t stream) {
+  if (G % kFlatBundle == 0 && G >= kFlatGroups) {
+    auto kernel = unpack_mixed_flat_kernel<T, ST>;
+    const int64_t flat_tasks = (N * G + kFlatGroups - 1) / kFlatGroups;
+    kernel<<<persistent_grid(kernel, kThreads, flat_tasks), kThreads, 0, stream>>>(
+        packed, bits, word_offsets, (const ST*)scale, (const ST*)mn, (T*)out, N * G, G);
+    return check_launch();
+  }
   const int64_t tasks = N * ((G + kBundle - 1) / kBundle);
   unpack_mixed_kernel<T, ST><<<persistent_grid(unpack_mixed_kernel<T, ST>, kThreads, tasks), kThreads, 0, stream>>>(
       packed, bits, word_offsets, (const ST*)scale, (const ST*)mn, (T*)out, N, G);
@@ -392,31 +737,42 @@ extern "C" int actnn_bits_prefix(const int32_t* bits, int64_t N, int64_t G, int6
   return check_launch();
 }
 
-extern "C" int actnn_pack_mixed(const void* data, const void* mn, const void* mx, const int32_t* bits,
-                                const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out,
-                                int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype,
-                                int stochastic, const void* noise, uint64_t seed, uint64_t offset,
-                                actnn_stream_t stream) {
+namespace actnn {
+// `min_is_exact`: every `mn[q]` is the true minimum of its group (then the rounding itself maps
+// the smallest values to code 0 and the lower clamp is dropped).
+int pack_mixed_impl(const void* data, const void* mn, const void* mx, const int32_t* bits,
+                    const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out, int64_t N, int64_t G,
+                    int64_t group_size, int dtype, int stat_dtype, int stochastic, const void* noise, uint64_t seed,
+                    uint64_t offset, bool min_is_exact, cudaStream_t s) {
   if (int st = check_common(N, G, group_size, dtype, stat_dtype)) return st;
   if (N == 0 || G == 0) return ACTNN_OK;
   if (!data || !mn || !mx || !bits || !word_offsets || !packed || !scale) return ACTNN_ERR_NULL;
   const size_t al = dtype == ACTNN_F32 ? 32 : 16;
   if (!aligned(data, al) || (noise && !aligned(noise, al)) || !aligned(packed, 4)) return ACTNN_ERR_ALIGN;
-  cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
     case ACTNN_F16:
       return launch_pack<__half, __half>(data, mn, mx, bits, word_offsets, packed, scale, mn_out, N, G,
-                                         stochastic, noise, seed, offset, s);
+                                         stochastic, noise, seed, offset, min_is_exact, s);
     case ACTNN_BF16:
       return launch_pack<__nv_bfloat16, __nv_bfloat16>(data, mn, mx, bits, word_offsets, packed, scale, mn_out,
-                                                       N, G, stochastic, noise, seed, offset, s);
+                                                       N, G, stochastic, noise, seed, offset, min_is_exact, s);
     default:
       if (stat_dtype == ACTNN_BF16)
         return launch_pack<float, __nv_bfloat16>(data, mn, mx, bits, word_offsets, packed, scale, mn_out, N, G,
-                                                 stochastic, noise, seed, offset, s);
+                                                 stochastic, noise, seed, offset, min_is_exact, s);
       return launch_pack<float, float>(data, mn, mx, bits, word_offsets, packed, scale, mn_out, N, G,
-                                       stochastic, noise, seed, offset, s);
+                                       stochastic, noise, seed, offset, min_is_exact, s);
   }
+}
+}  // namespace actnn
+
+extern "C" int actnn_pack_mixed(const void* data, const void* mn, const void* mx, const int32_t* bits,
+                                const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out,
+                                int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype,
+                                int stochastic, const void* noise, uint64_t seed, uint64_t offset,
+                                actnn_stream_t stream) {
+  return pack_mixed_impl(data, mn, mx, bits, word_offsets, packed, scale, mn_out, N, G, group_size, dtype,
+                         stat_dtype, stochastic, noise, seed, offset, false, (cudaStream_t)stream);
 }
 
 extern "C" int actnn_unpack_mixed(const int32_t* packed, const int32_t* bits, const int64_t* word_offsets,

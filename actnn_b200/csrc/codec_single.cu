@@ -23,11 +23,12 @@ constexpr int kThreads = 256;
 // constant that is subtracted up front, so no per-code masking is needed.
 template <typename T, int BITS> struct ByteAcc {
   static constexpr int WPT = 8 / BITS;
-  static constexpr int R = MagicInfo<T>::paired ? 4 : 8;
+  using Fmt = MagicFmt<T, BITS>;
+  static constexpr int R = Fmt::paired ? 4 : 8;
   uint32_t a[R];
   ACTNN_DEV ByteAcc() {
 #pragma unroll
-    for (int i = 0; i < R; ++i) a[i] = 0u - shifted_sum(MagicInfo<T>::bias, BITS, WPT);
+    for (int i = 0; i < R; ++i) a[i] = 0u - shifted_sum(Fmt::bias, BITS, WPT);
   }
   template <int NI> ACTNN_DEV void add(const Magic<T>& m) {
 #pragma unroll
@@ -35,11 +36,11 @@ template <typename T, int BITS> struct ByteAcc {
   }
   template <int NI> ACTNN_DEV void add_missing() {       // a sample past the end: code 0 everywhere
 #pragma unroll
-    for (int i = 0; i < R; ++i) a[i] += MagicInfo<T>::bias << (NI * BITS);
+    for (int i = 0; i < R; ++i) a[i] += Fmt::bias << (NI * BITS);
   }
   ACTNN_DEV uint2 bytes() const {
     uint2 w;
-    if constexpr (MagicInfo<T>::paired) {                // a[k] = byte 2k | byte 2k+1 << 16
+    if constexpr (Fmt::paired) {                         // a[k] = byte 2k | byte 2k+1 << 16
       w.x = __byte_perm(a[0], a[1], 0x6420);
       w.y = __byte_perm(a[2], a[3], 0x6420);
     } else {                                             // a[j] = byte j

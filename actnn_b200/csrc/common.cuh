@@ -139,16 +139,20 @@ ACTNN_DEV float warp_max(float v) {
 // Lane r holds row r of a 32x32 bit matrix (bit c = column c).  Afterwards lane r holds
 // column r of the original (bit c = original lane c, bit r).  Five butterfly stages; per
 // stage one shuffle, one funnel shift (a rotate) and one LOP3 bit-select.
+// The stages that exchange half-words and bytes are one byte-permute each.
 struct TransposePlan {
-  uint32_t keep[5];   // bits this lane keeps at stage s = 16, 8, 4, 2, 1
-  uint32_t rot[5];    // left-rotate applied to the partner's word
+  uint32_t sel16, sel8;   // byte selectors of the stages s = 16 and s = 8
+  uint32_t keep[3];       // bits this lane keeps at stage s = 4, 2, 1
+  uint32_t rot[3];        // left-rotate applied to the partner's word
 };
 ACTNN_DEV TransposePlan make_transpose_plan(int lane) {
   TransposePlan p;
-  const uint32_t m[5] = {0x0000ffffu, 0x00ff00ffu, 0x0f0f0f0fu, 0x33333333u, 0x55555555u};
+  p.sel16 = (lane & 16) ? 0x3276u : 0x5410u;
+  p.sel8 = (lane & 8) ? 0x3715u : 0x6240u;
+  const uint32_t m[3] = {0x0f0f0f0fu, 0x33333333u, 0x55555555u};
 #pragma unroll
-  for (int k = 0; k < 5; ++k) {
-    const int s = 16 >> k;
+  for (int k = 0; k < 3; ++k) {
+    const int s = 4 >> k;
     const bool low = (lane & s) == 0;
     p.keep[k] = low ? m[k] : ~m[k];
     p.rot[k] = low ? s : 32 - s;
@@ -156,9 +160,11 @@ ACTNN_DEV TransposePlan make_transpose_plan(int lane) {
   return p;
 }
 ACTNN_DEV uint32_t warp_transpose32(uint32_t x, const TransposePlan& p) {
+  x = __byte_perm(x, __shfl_xor_sync(kFull, x, 16), p.sel16);
+  x = __byte_perm(x, __shfl_xor_sync(kFull, x, 8), p.sel8);
 #pragma unroll
-  for (int k = 0; k < 5; ++k) {
-    const uint32_t y = __shfl_xor_sync(kFull, x, 16 >> k);
+  for (int k = 0; k < 3; ++k) {
+    const uint32_t y = __shfl_xor_sync(kFull, x, 4 >> k);
     const uint32_t ry = __funnelshift_l(y, y, p.rot[k]);
     x = (x & p.keep[k]) | (ry & ~p.keep[k]);
   }
@@ -213,9 +219,12 @@ ACTNN_DEV Philox4 noise_call(const NoiseKey& key, uint64_t c) {
 // flat group q, position d in the group, lane t = d / 8, j = d % 8.
 //   counter = (lo32(c), hi32(c), lo32(offset), hi32(offset)), key = (lo32(seed), hi32(seed));
 //   the call's four output words v[0..3] are extended to eight, e[i] = v[i] and
-//   e[4 + i] = v[i] ^ rotl32(v[(i + 1) % 4], 11) (see quant_math.cuh for why that is sound);
-//   16-bit activations: c = (q / 4) * 32 + t; byte j of the word pair (e[2h], e[2h + 1]),
-//     h = q % 4, is k in [0, 255]; noise = (2k + 1 - 256) / 512.
+//   e[4 + i] = v[i] + 0x9E3779B1 * v[(i + 1) % 4] mod 2^32 (see quant_math.cuh for why that
+//   is sound);
+//   16-bit activations: c = (q / 4) * 32 + t; word w = e[2h + j / 4], h = q % 4, p = j % 4;
+//     float16:  k = bits 1..8 (p even) or 17..24 (p odd) of w rotated right by 8 * (p / 2);
+//     bfloat16: k = byte 2 * (p % 2) + p / 2 of w;
+//     noise = (2k + 1 - 256) / 512.
 //   float32 activations: c = (q / 2) * 32 + t; 16-bit field j of the words e[4h .. 4h + 3],
 //     h = q % 2, is k; noise = (2k + 1 - 65536) / 131072.
 // Both are odd multiples of the step, symmetric about zero, strictly inside (-0.5, 0.5)
@@ -227,6 +236,13 @@ struct DeviceInfo { int sm_count; };
 const DeviceInfo& device_info();                   // api.cu (per current device, cached)
 int check_launch();                                // api.cu: cudaPeekAtLastError -> status
 unsigned* bulk_wait_counter();                     // api.cu: device counter of bulk-copy waits that gave up
+
+// codec_mixed.cu: actnn_pack_mixed with one more promise from the caller, `min_is_exact`
+// (every mn[q] is the true minimum of its group, as after actnn_minimax).
+int pack_mixed_impl(const void* data, const void* mn, const void* mx, const int32_t* bits,
+                    const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out, int64_t N, int64_t G,
+                    int64_t group_size, int dtype, int stat_dtype, int stochastic, const void* noise, uint64_t seed,
+                    uint64_t offset, bool min_is_exact, cudaStream_t stream);
 
 static inline bool aligned(const void* p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 

@@ -38,8 +38,8 @@ extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* sca
   st = actnn_calc_precision(C_out, nullptr, N, initial_bits, target, bits_out, word_offsets_out, G, group_size,
                             nullptr, 0, stream);
   if (st) return st;
-  return actnn_pack_mixed(data, mn, mx, bits_out, word_offsets_out, packed, scale, mn_out, N, G, group_size, dtype,
-                          stat_dtype, stochastic, noise, seed, offset, stream);
+  return pack_mixed_impl(data, mn, mx, bits_out, word_offsets_out, packed, scale, mn_out, N, G, group_size, dtype,
+                         stat_dtype, stochastic, noise, seed, offset, true, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -130,16 +130,24 @@ template <> ACTNN_DEV void oct_minmax<__nv_bfloat16>(const Oct<__nv_bfloat16>& o
 // Philox fields -> eight noise values in the register format of Oct<T>.
 //   16-bit types: `w0`, `w1` hold the eight bytes k0..k7 of this group's half of a call.
 //   float32:      `v` holds the four words of the group's call (eight 16-bit fields).
+// Both 16-bit formats count linearly through their subnormals and first normal binade: the
+// bit pattern v < 2^11 (float16) or v < 2^8 (bfloat16) IS the value v * 2^-24 resp.
+// v * 2^-133.  A random field masked in place is therefore already a number proportional to
+// it, and one exact fused multiply-add turns it into the centred noise: one logic
+// instruction and one HFMA2 per two elements.
 ACTNN_DEV Oct<__half> noise_from_bytes_f16(uint32_t w0, uint32_t w1) {
-  // half bits 0x6001 | (k << 1) = 512 + k + 0.5; times 2^-8, minus 2.5 = (2k + 1 - 256) / 512
-  const __half2 s = __halves2half2(__ushort_as_half(0x1C00), __ushort_as_half(0x1C00));   // 2^-8
-  const __half2 c = __halves2half2(__ushort_as_half(0xC100), __ushort_as_half(0xC100));   // -2.5
+  // bits (2k + 1) = (2k + 1) * 2^-24; times 2^15, minus 0.5 = (2k + 1 - 256) / 512.
+  // Elements 0, 1 take k from bits 1..8 and 17..24 of the word, elements 2, 3 from the same
+  // bits of the word rotated right by 8; every bit of the word is used exactly once.
+  const uint32_t s_bits = 0x78007800u, c_bits = 0xB800B800u;                     // 2^15, -0.5
+  const __half2 s = *reinterpret_cast<const __half2*>(&s_bits);
+  const __half2 c = *reinterpret_cast<const __half2*>(&c_bits);
   Oct<__half> o;
-  const uint32_t sp[4] = {__byte_perm(w0, 0u, 0x4140), __byte_perm(w0, 0u, 0x4342),
-                          __byte_perm(w1, 0u, 0x4140), __byte_perm(w1, 0u, 0x4342)};
 #pragma unroll
   for (int m = 0; m < 4; ++m) {
-    const uint32_t bits = sp[m] * 2u + 0x60016001u;
+    const uint32_t w = (m < 2) ? w0 : w1;
+    const uint32_t r = (m & 1) ? __funnelshift_r(w, w, 8) : w;
+    const uint32_t bits = (r & 0x01FE01FEu) | 0x00010001u;
     const __half2 h = __hfma2(*reinterpret_cast<const __half2*>(&bits), s, c);
     o.r[m] = *reinterpret_cast<const uint32_t*>(&h);
   }
@@ -150,14 +158,17 @@ ACTNN_DEV float noise_float(uint32_t k, float step, float bias) {
   return __fmaf_rn(__uint_as_float(0x4B000000u + 2u * k + 1u), step, bias);
 }
 ACTNN_DEV Oct<__nv_bfloat16> noise_from_bytes_bf16(uint32_t w0, uint32_t w1) {
+  // bits k = k * 2^-133; times 2^125, minus 255/512 = (2k + 1 - 256) / 512.
+  // Elements 0, 1 take bytes 0 and 2 of the word, elements 2, 3 bytes 1 and 3.
+  const uint32_t s_bits = 0x7E007E00u, c_bits = 0xBEFFBEFFu;                     // 2^125, -255/512
+  const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(&s_bits);
+  const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&c_bits);
   Oct<__nv_bfloat16> o;
 #pragma unroll
   for (int m = 0; m < 4; ++m) {
     const uint32_t w = (m < 2) ? w0 : w1;
-    const uint32_t ka = (w >> (16 * (m & 1))) & 0xffu, kb = (w >> (16 * (m & 1) + 8)) & 0xffu;
-    // (2^23 + 2k + 1) / 512 - 16384.5 = (2k + 1 - 256) / 512
-    const __nv_bfloat162 h = __floats2bfloat162_rn(noise_float(ka, 1.0f / 512.0f, -16384.5f),
-                                                   noise_float(kb, 1.0f / 512.0f, -16384.5f));
+    const uint32_t bits = (m & 1) ? __byte_perm(w, 0u, 0x4341) : (w & 0x00FF00FFu);
+    const __nv_bfloat162 h = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&bits), s, c);
     o.r[m] = *reinterpret_cast<const uint32_t*>(&h);
   }
   return o;
@@ -173,19 +184,21 @@ ACTNN_DEV Oct<float> noise_from_fields_f32(const Philox4& v) {
   return o;
 }
 
-// One Philox call yields four words; four more are derived as v[i] ^ rotl(v[i+1], 11).  Any
-// two of the eight words are jointly uniform (the derived word's partner enters only it and
-// its own original), hence any two of the 32 bytes are independent and uniform: second-order
-// statistics of the rounding noise equal those of independent noise at half the generator
-// cost.  A call thus serves one lane for four neighbouring groups (16-bit activations, one
-// byte per element) or two groups (float32, 16 bits per element).
+// One Philox call yields four words; four more are derived as v[i] + M * v[i+1] (mod 2^32,
+// M odd: one integer multiply-add each).  Any two of the eight words are jointly uniform:
+// (x, y) -> (x, x + M*y) and (x, y, z) -> (x + M*y, y + M*z) are onto with uniform fibres,
+// hence any two noise fields are independent and uniform and second-order statistics of the
+// rounding noise equal those of independent noise at half the generator cost.  A call thus
+// serves one lane for four neighbouring groups (16-bit activations, one byte per element) or
+// two groups (float32, 16 bits per element).
 struct NoiseWords { uint32_t e[8]; };
+constexpr uint32_t kNoiseMul = 0x9E3779B1u;
 ACTNN_DEV NoiseWords expand_call(const Philox4& p) {
   NoiseWords w;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     w.e[i] = p.v[i];
-    w.e[4 + i] = p.v[i] ^ __funnelshift_l(p.v[(i + 1) & 3], p.v[(i + 1) & 3], 11);
+    w.e[4 + i] = p.v[(i + 1) & 3] * kNoiseMul + p.v[i];
   }
   return w;
 }
@@ -242,8 +255,9 @@ ACTNN_DEV void noise_block(const NoiseKey& key, uint64_t q, int lane, Oct<T> (&o
 // ------------------------------------------------------------------ quantize one octet
 // The result stays in "magic" form: the registers still carry the exponent bits of the
 // rounding constant, code in the low mantissa bits.
-//   float16:            4 registers, two elements each: halves = 0x6600 + code
-//   float32 / bfloat16: 8 registers, one element each:  0x4B400000 + code
+//   float16:                    4 registers, two elements each: halves = 0x6600 + code
+//   bfloat16, up to 6 bits:     4 registers, two elements each: halves = 0x4340 + code
+//   float32 / bfloat16, 7-8 b.: 8 registers, one element each:  0x4B400000 + code
 // Because those high bits are the same for every element, shifted sums of magic registers
 // equal shifted sums of the codes plus a compile-time constant (mod 2^32): rows and bytes
 // are assembled with integer multiply-adds and one constant, without masking each code.
@@ -251,6 +265,24 @@ template <typename T> struct Magic { uint32_t v[8]; };
 template <> struct Magic<__half> { uint32_t v[4]; };
 template <typename T> struct MagicInfo { static constexpr uint32_t bias = 0x4B400000u; static constexpr bool paired = false; };
 template <> struct MagicInfo<__half> { static constexpr uint32_t bias = 0x66006600u; static constexpr bool paired = true; };
+// The form actually produced for a given width.
+template <typename T, int B> struct MagicFmt {
+  static constexpr bool paired = false;
+  static constexpr uint32_t bias = 0x4B400000u;
+  static constexpr uint32_t code_mask = 0x1ffu;
+};
+template <int B> struct MagicFmt<__half, B> {
+  static constexpr bool paired = true;
+  static constexpr uint32_t bias = 0x66006600u;
+  static constexpr uint32_t code_mask = 0x01ff01ffu;
+};
+template <int B> struct MagicFmt<__nv_bfloat16, B> {
+  // 192 + t lies in [128, 256) for t in [-0.5, 63.5], where bfloat16 has spacing 1: the packed
+  // add rounds to the nearest integer, ties to even, exactly like rint; 7 and 8 bits need float32
+  static constexpr bool paired = B <= 6;
+  static constexpr uint32_t bias = paired ? 0x43404340u : 0x4B400000u;
+  static constexpr uint32_t code_mask = paired ? 0x003f003fu : 0x1ffu;
+};
 
 // CLAMP_LOW = false may be used when min really is the group minimum: then
 // (x - mn') * scale + noise >= -0.5 always and the round-to-even of the magic add maps it
@@ -292,9 +324,10 @@ ACTNN_DEV Magic<T> quantize_oct(const Oct<T>& x, const Oct<T>& nz, const QP<T>& 
     // bfloat16 patterns of 2^BITS - 1
     constexpr uint32_t kB[9] = {0, 0x3F803F80u, 0x40404040u, 0x40E040E0u, 0x41704170u, 0x41F841F8u,
                                 0x427C427Cu, 0x42FE42FEu, 0x437F437Fu};
-    const uint32_t b_bits = kB[BITS], zero_bits = 0u;
+    const uint32_t b_bits = kB[BITS], zero_bits = 0u, magic_bits = 0x43404340u;   // 192
     const __nv_bfloat162 B2 = *reinterpret_cast<const __nv_bfloat162*>(&b_bits);
     const __nv_bfloat162 zero2 = *reinterpret_cast<const __nv_bfloat162*>(&zero_bits);
+    const __nv_bfloat162 magic2 = *reinterpret_cast<const __nv_bfloat162*>(&magic_bits);
     const __nv_bfloat162* xv = reinterpret_cast<const __nv_bfloat162*>(x.r);
     const __nv_bfloat162* nv = reinterpret_cast<const __nv_bfloat162*>(nz.r);
 #pragma unroll
@@ -303,11 +336,16 @@ ACTNN_DEV Magic<T> quantize_oct(const Oct<T>& x, const Oct<T>& nz, const QP<T>& 
       t = __hadd2_rn(t, nv[k]);
       if (CLAMP_LOW) t = __hmax2(t, zero2);
       t = __hmin2(t, B2);                                   // NaN -> B
-      const uint32_t u = *reinterpret_cast<const uint32_t*>(&t);
-      // bfloat16 -> float32 is a shift; 8 mantissa bits cannot hold 255 plus a round bit, so
-      // the integer rounding runs in float32 (1.5 * 2^23 also absorbs t in [-0.5, 0))
-      m.v[2 * k] = __float_as_uint(__fadd_rn(__uint_as_float(u << 16), 12582912.f));
-      m.v[2 * k + 1] = __float_as_uint(__fadd_rn(__uint_as_float(u & 0xffff0000u), 12582912.f));
+      if constexpr (MagicFmt<T, BITS>::paired) {
+        t = __hadd2_rn(t, magic2);
+        m.v[k] = *reinterpret_cast<const uint32_t*>(&t);
+      } else {
+        const uint32_t u = *reinterpret_cast<const uint32_t*>(&t);
+        // bfloat16 -> float32 is a shift; 8 mantissa bits cannot hold 255 plus a round bit, so
+        // the integer rounding runs in float32 (1.5 * 2^23 also absorbs t in [-0.5, 0))
+        m.v[2 * k] = __float_as_uint(__fadd_rn(__uint_as_float(u << 16), 12582912.f));
+        m.v[2 * k + 1] = __float_as_uint(__fadd_rn(__uint_as_float(u & 0xffff0000u), 12582912.f));
+      }
     }
   }
   return m;
@@ -346,8 +384,8 @@ constexpr uint32_t shifted_sum(uint32_t c, int step, int count) {
 // lo = bits 0..31, hi = bits 32..63 (only B > 4 reaches hi).
 template <typename T, int B> ACTNN_DEV void row_from_magic(const Magic<T>& m, uint32_t& lo, uint32_t& hi) {
   hi = 0u;
-  if constexpr (MagicInfo<T>::paired) {
-    constexpr uint32_t bias = MagicInfo<T>::bias;
+  if constexpr (MagicFmt<T, B>::paired) {
+    constexpr uint32_t bias = MagicFmt<T, B>::bias;
     if constexpr (B <= 2) {
       // even elements accumulate in the low half, odd ones in the high half
       uint32_t acc = m.v[0] + (m.v[1] << (2 * B)) + (m.v[2] << (4 * B)) + (m.v[3] << (6 * B));
@@ -363,7 +401,7 @@ template <typename T, int B> ACTNN_DEV void row_from_magic(const Magic<T>& m, ui
       uint32_t S[2] = {0u, 0u};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const uint32_t c = m.v[k] & 0x01ff01ffu;
+        const uint32_t c = m.v[k] & MagicFmt<T, B>::code_mask;
         const uint32_t pr = (c | (c >> (16 - B))) & ((1u << (2 * B)) - 1u);
         if (k == 0) put_bits<0 * B, 2 * B>(S, pr);
         if (k == 1) put_bits<2 * B, 2 * B>(S, pr);
@@ -373,7 +411,7 @@ template <typename T, int B> ACTNN_DEV void row_from_magic(const Magic<T>& m, ui
       lo = S[0]; hi = S[1];
     }
   } else {
-    constexpr uint32_t bias = MagicInfo<T>::bias;
+    constexpr uint32_t bias = MagicFmt<T, B>::bias;
     if constexpr (B <= 4) {
       uint32_t acc = m.v[0];
 #pragma unroll

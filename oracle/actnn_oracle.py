@@ -543,10 +543,10 @@ def _philox_calls(count: int, seed: int, offset: int) -> np.ndarray:
 
 
 def _expand_call(r: np.ndarray) -> np.ndarray:
-    """Eight words per call: the four outputs and ``v[i] ^ rotl32(v[(i + 1) % 4], 11)``."""
-    nxt = np.roll(r, -1, axis=1)
-    rot = ((nxt << np.uint32(11)) | (nxt >> np.uint32(21))).astype(np.uint32)
-    return np.concatenate([r, r ^ rot], axis=1)
+    """Eight words per call: the four outputs and ``v[i] + 0x9E3779B1 * v[(i + 1) % 4]`` mod 2^32."""
+    nxt = np.roll(r, -1, axis=1).astype(np.uint64)
+    derived = (r.astype(np.uint64) + nxt * np.uint64(0x9E3779B1)) & np.uint64(0xFFFFFFFF)
+    return np.concatenate([r, derived.astype(np.uint32)], axis=1)
 
 
 def philox_noise(numel: int, dtype: torch.dtype, seed: int, offset: int) -> torch.Tensor:
@@ -555,8 +555,10 @@ def philox_noise(numel: int, dtype: torch.dtype, seed: int, offset: int) -> torc
     Element ``e`` of the padded ``[N, G, 256]`` activation: flat group ``q = e // 256``,
     position ``d = e % 256``, lane ``t = d // 8``, ``j = d % 8``.  Each call's four output
     words are extended to eight (``_expand_call``).
-    * float16 / bfloat16: call ``c = (q // 4) * 32 + t``; with ``h = q % 4``, byte ``j`` of the
-      word pair ``(e[2h], e[2h + 1])`` is ``k``; noise ``(2k + 1 - 256) / 512``.
+    * float16 / bfloat16: call ``c = (q // 4) * 32 + t``; with ``h = q % 4`` and ``p = j % 4`` the
+      word is ``w = e[2h + j // 4]``.  float16: ``k`` = bits 1..8 (``p`` even) or 17..24 (``p`` odd)
+      of ``w`` rotated right by ``8 * (p // 2)``; bfloat16: ``k`` = byte ``2 * (p % 2) + p // 2`` of
+      ``w``.  Noise ``(2k + 1 - 256) / 512``.
     * float32: call ``c = (q // 2) * 32 + t``; with ``h = q % 2``, 16-bit field ``j`` of the
       words ``e[4h .. 4h + 3]`` is ``k``; noise ``(2k + 1 - 65536) / 131072``.
     """
@@ -571,7 +573,14 @@ def philox_noise(numel: int, dtype: torch.dtype, seed: int, offset: int) -> torc
     else:
         c, h = (q // 4) * 32 + t, q % 4
         w = _expand_call(_philox_calls(int(c.max()) + 1 if numel else 0, seed, offset))
-        k = (w[c, 2 * h + j // 4] >> (8 * (j % 4)).astype(np.uint32)) & np.uint32(0xFF)
+        word = w[c, 2 * h + j // 4].astype(np.uint64)
+        p = j % 4
+        if dtype == torch.float16:
+            rot = (8 * (p // 2)).astype(np.uint64)
+            word = ((word >> rot) | (word << (np.uint64(32) - rot))) & np.uint64(0xFFFFFFFF)
+            k = (word >> (1 + 16 * (p % 2)).astype(np.uint64)) & np.uint64(0xFF)
+        else:
+            k = (word >> (8 * (2 * (p % 2) + p // 2)).astype(np.uint64)) & np.uint64(0xFF)
         u = (2.0 * k.astype(np.float64) + 1 - 256) / 512
     return torch.from_numpy(u.astype(np.float32)).to(dtype)
 
