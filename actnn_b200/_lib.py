@@ -45,6 +45,7 @@ SIGNATURES = {
     "actnn_max_pool2d_backward": [_P, _P, _P, _L, _L, _L, _L] + [_I] * 9 + [_P],
     "actnn_noise_fill": [_P, _L, _I, _U, _U, _P],
     "actnn_bulk_wait_failures": [_P],
+    "actnn_bad_width_bundles": [_P],
     "actnn_batch_norm_stats": [_P, _P, _P, _L, _L, _L, _D, _I, _P, _L, _P],
     "actnn_batch_norm_elemt": [_P] * 6 + [_L, _L, _L, _I, _P, _L, _P],
     "actnn_batch_norm_backward_reduce": [_P] * 8 + [_L, _L, _L, _I, _P, _L, _P],

@@ -19,30 +19,42 @@ from .. import _lib
 aten = torch.ops.aten
 
 
+class _cudnn_benchmark:
+    """``torch.backends.cudnn.benchmark = flag`` for the duration of a call; the global is only
+    touched when it differs (the usual case, one setting for a whole run, costs nothing)."""
+
+    def __init__(self, flag):
+        self.flag = bool(flag)
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.backends.cudnn.benchmark
+        if cur != self.flag:
+            self.prev = cur
+            torch.backends.cudnn.benchmark = self.flag
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.backends.cudnn.benchmark = self.prev
+        return False
+
+
 def cudnn_convolution_backward(input, grad_output, weight, padding, stride, dilation, groups,
                                benchmark, deterministic, allow_tf32, output_mask):
-    prev = torch.backends.cudnn.benchmark
-    torch.backends.cudnn.benchmark = bool(benchmark)
-    try:
+    with _cudnn_benchmark(benchmark):
         gi, gw, _ = aten.convolution_backward(
             grad_output, input, weight, None, list(stride), list(padding), list(dilation), False,
             [0] * len(stride), groups, [bool(output_mask[0]), bool(output_mask[1]), False])
-    finally:
-        torch.backends.cudnn.benchmark = prev
     return gi, gw
 
 
 def cudnn_convolution_transpose_backward(input, grad_output, weight, padding, output_padding, stride,
                                          dilation, groups, benchmark, deterministic, allow_tf32,
                                          output_mask):
-    prev = torch.backends.cudnn.benchmark
-    torch.backends.cudnn.benchmark = bool(benchmark)
-    try:
+    with _cudnn_benchmark(benchmark):
         gi, gw, _ = aten.convolution_backward(
             grad_output, input, weight, None, list(stride), list(padding), list(dilation), True,
             list(output_padding), groups, [bool(output_mask[0]), bool(output_mask[1]), False])
-    finally:
-        torch.backends.cudnn.benchmark = prev
     return gi, gw
 
 
@@ -138,9 +150,10 @@ def batch_norm_elemt(input, weight, bias, mean, invstd, eps):
     N, C, HW = _bn_dims(x)
     y = torch.empty_like(x)
     ws = torch.empty(max(16 * C, 16), dtype=torch.uint8, device=x.device)
-    _lib.call("actnn_batch_norm_elemt", x, _lib.ptr(x), _lib.ptr(_as_f32(weight)), _lib.ptr(_as_f32(bias)),
-              _lib.ptr(_as_f32(mean)), _lib.ptr(_as_f32(invstd)), _lib.ptr(y), N, C, HW, _lib.dtype_id(x.dtype),
-              _lib.ptr(ws), 16 * C, _lib.stream_of(x))
+    # the converted copies must outlive the call: a pointer taken from a temporary would dangle
+    w32, b32, m32, i32 = _as_f32(weight), _as_f32(bias), _as_f32(mean), _as_f32(invstd)
+    _lib.call("actnn_batch_norm_elemt", x, _lib.ptr(x), _lib.ptr(w32), _lib.ptr(b32), _lib.ptr(m32), _lib.ptr(i32),
+              _lib.ptr(y), N, C, HW, _lib.dtype_id(x.dtype), _lib.ptr(ws), 16 * C, _lib.stream_of(x))
     return y
 
 
@@ -159,8 +172,9 @@ def batch_norm_backward_reduce(grad_out, input, mean, invstd, weight, input_g, w
         raise RuntimeError("batch_norm_backward_reduce: out must be a contiguous float32 tensor of >= 2*C elements")
     grad_weight = torch.empty(C, dtype=torch.float32, device=x.device)
     ws, nbytes = _bn_workspace(N, C, HW, x.device)
-    _lib.call("actnn_batch_norm_backward_reduce", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(_as_f32(weight)),
-              _lib.ptr(_as_f32(mean)), _lib.ptr(_as_f32(invstd)), out.data_ptr(), out.data_ptr() + 4 * C,
+    w32, m32, i32 = _as_f32(weight), _as_f32(mean), _as_f32(invstd)       # kept alive across the call
+    _lib.call("actnn_batch_norm_backward_reduce", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(w32),
+              _lib.ptr(m32), _lib.ptr(i32), out.data_ptr(), out.data_ptr() + 4 * C,
               _lib.ptr(grad_weight), N, C, HW, _lib.dtype_id(x.dtype), _lib.ptr(ws), nbytes, _lib.stream_of(x))
     flat = out.view(-1)
     sum_dy, sum_dy_xmu = flat[:C], flat[C:2 * C]
@@ -182,9 +196,11 @@ def batch_norm_backward_elemt(grad_out, input, mean, invstd, weight, sum_dy, sum
     counts = count.reshape(-1).to(torch.float32).contiguous()
     dx = torch.empty_like(x)
     ws = torch.empty(max(16 * C, 16), dtype=torch.uint8, device=x.device)
-    _lib.call("actnn_batch_norm_backward_elemt", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(_as_f32(weight)),
-              _lib.ptr(_as_f32(mean)), _lib.ptr(_as_f32(invstd)), _lib.ptr(sum_dy.contiguous()),
-              _lib.ptr(sum_dy_xmu.contiguous()), _lib.ptr(counts), counts.numel(), _lib.ptr(dx), N, C, HW,
+    w32, m32, i32 = _as_f32(weight), _as_f32(mean), _as_f32(invstd)       # kept alive across the call
+    sdy, sdx = _as_f32(sum_dy), _as_f32(sum_dy_xmu)
+    _lib.call("actnn_batch_norm_backward_elemt", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(w32),
+              _lib.ptr(m32), _lib.ptr(i32), _lib.ptr(sdy),
+              _lib.ptr(sdx), _lib.ptr(counts), counts.numel(), _lib.ptr(dx), N, C, HW,
               _lib.dtype_id(x.dtype), _lib.ptr(ws), 16 * C, _lib.stream_of(x))
     return dx
 

@@ -109,7 +109,7 @@ def compress_mixed_precision(data, target_bits: int, initial_bits: int, range_fa
     bits = torch.empty(n, dtype=torch.int32, device=dev)
     offsets = torch.empty(n + 1, dtype=torch.int64, device=dev)
     C = torch.empty(n, dtype=torch.float32, device=dev)
-    ws_bytes = 2 * ((n * g * data.element_size() + 255) // 256 * 256)
+    ws_bytes = 2 * ((n * g * data.element_size() + 255) // 256 * 256) + 256     # actnn_compress_mixed_workspace
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     if grad_scale is not None and (grad_scale.dtype != torch.float32 or not grad_scale.is_cuda
                                    or grad_scale.numel() != 1):

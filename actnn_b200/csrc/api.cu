@@ -1,4 +1,5 @@
 // Status strings, cached device properties, launch checking and the noise export.
+#include <atomic>
 #include <mutex>
 
 #include "quant_math.cuh"
@@ -7,17 +8,24 @@ namespace actnn {
 
 const DeviceInfo& device_info() {
   // Immutable per-device facts, filled on first use.  Racing first calls write the same
-  // values, so no lock is needed.
+  // values; the flag is published with release / acquire so that a reader that sees it set
+  // also sees the value.
   static DeviceInfo info[64];
-  static bool ready[64];
+  static std::atomic<bool> ready[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  if (!ready[dev]) {
+  if (!ready[dev].load(std::memory_order_acquire)) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    info[dev].sm_count = sms;
-    ready[dev] = true;
+    DeviceInfo fresh;
+    fresh.sm_count = sms;
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!ready[dev].load(std::memory_order_relaxed)) {
+      info[dev] = fresh;
+      ready[dev].store(true, std::memory_order_release);
+    }
   }
   return info[dev];
 }
@@ -27,15 +35,19 @@ const DeviceInfo& device_info() {
 __device__ unsigned g_bulk_wait_gave_up;
 
 unsigned* bulk_wait_counter() {
-  static unsigned* addr[64];
+  static std::atomic<unsigned*> addr[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  if (!addr[dev]) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_bulk_wait_gave_up) == cudaSuccess) addr[dev] = (unsigned*)p;
+  unsigned* p = addr[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void* q = nullptr;
+    if (cudaGetSymbolAddress(&q, g_bulk_wait_gave_up) == cudaSuccess) {
+      p = (unsigned*)q;
+      addr[dev].store(p, std::memory_order_release);
+    }
   }
-  return addr[dev];
+  return p;
 }
 
 // cudaGetLastError also clears a launch error, so one refused launch does not fail every later call.

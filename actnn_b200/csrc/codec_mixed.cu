@@ -53,6 +53,9 @@ struct BundleWalker {
   }
 };
 
+// Device counter of bundles whose width was outside 1..8 (nothing is written for them).
+__device__ unsigned g_bad_width_bundles;
+
 // ---------------------------------------------------------------------------- pack
 // Groups per pack bundle: eight octets per lane for 16-bit types, four for float32.
 template <typename T> struct PackShape { static constexpr int GPB = sizeof(T) == 2 ? 8 : 4; };
@@ -147,7 +150,9 @@ pack_mixed_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T*
     switch (b) {
       ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
       ACTNN_CASE(8)
-      default: break;     // widths outside 1..8 are skipped; the host documents the range
+      default:            // widths outside 1..8: nothing is written, the bundle is counted
+        if (lane == 0) atomicAdd(&g_bad_width_bundles, 1u);
+        break;
     }
 #undef ACTNN_CASE
   }
@@ -167,9 +172,6 @@ pack_mixed_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T*
 constexpr int kFlatGroups = 32;       // groups per task
 constexpr int kFlatBundle = 4;        // groups per bundle
 enum NoiseMode { kNoisePhilox = 0, kNoiseTensor = 1, kNoiseNone = 2 };
-
-// Device counter of bundles whose width was outside 1..8 (nothing is written for them).
-__device__ unsigned g_bad_width_bundles;
 
 // (mn', scale) of the lane's own group in the form the quantizer consumes.
 template <typename T> struct LaneParams { uint32_t a, b; };
@@ -773,6 +775,12 @@ extern "C" int actnn_pack_mixed(const void* data, const void* mn, const void* mx
                                 actnn_stream_t stream) {
   return pack_mixed_impl(data, mn, mx, bits, word_offsets, packed, scale, mn_out, N, G, group_size, dtype,
                          stat_dtype, stochastic, noise, seed, offset, false, (cudaStream_t)stream);
+}
+
+extern "C" int actnn_bad_width_bundles(uint32_t* count) {
+  if (!count) return ACTNN_ERR_NULL;
+  return cudaMemcpyFromSymbol(count, g_bad_width_bundles, sizeof(unsigned)) == cudaSuccess ? ACTNN_OK
+                                                                                           : ACTNN_ERR_LAUNCH;
 }
 
 extern "C" int actnn_unpack_mixed(const int32_t* packed, const int32_t* bits, const int64_t* word_offsets,

@@ -244,6 +244,19 @@ int pack_mixed_impl(const void* data, const void* mn, const void* mx, const int3
                     int64_t group_size, int dtype, int stat_dtype, int stochastic, const void* noise, uint64_t seed,
                     uint64_t offset, bool min_is_exact, cudaStream_t stream);
 
+// stats.cu: actnn_minimax with two extras for the one-call compress: rows walked from the
+// last to the first (`reverse`), and a word zeroed by the kernel (`clear_word`, the ticket of
+// the next kernel).
+int minimax_impl(const void* data, void* mn, void* mx, int64_t rows, int64_t cols, int dtype, int reverse,
+                 unsigned* clear_word, cudaStream_t stream);
+// stats.cu: sensitivities (actnn_range_sqr) and the greedy allocation (actnn_calc_precision, unit
+// weights, with word offsets) of one layer in one launch; `ticket` must be zero when it starts
+// and is zero again when it ends.
+bool range_greedy_supported(int64_t N, int initial_bits);
+int range_greedy_impl(const void* mn, const void* mx, int64_t N, int64_t G, int stat_dtype, float range_factor,
+                      float coeff, const float* grad_scale, float* C, unsigned* ticket, int initial_bits,
+                      double target, int32_t* b_out, int64_t* word_offsets, int64_t group_size, cudaStream_t stream);
+
 static inline bool aligned(const void* p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 
 #ifdef __CUDACC__

@@ -1,17 +1,21 @@
 // The whole adaptive (per-sample bit width) compress of one activation behind one call:
 // per-group min/max -> per-sample sensitivity -> greedy bit allocation -> scale, stochastic
-// rounding and mixed-precision pack.  Four kernel launches on the caller's stream, no host
+// rounding and mixed-precision pack.  Three kernel launches on the caller's stream, no host
 // synchronisation, no allocation: the per-group min / max that only live between the first
 // and the last kernel go to a workspace the caller provides.
+#include <atomic>
+
 #include "quant_math.cuh"
 
 using namespace actnn;
 
 extern "C" int64_t actnn_compress_mixed_workspace(int64_t N, int64_t G, int dtype) {
   if (N < 0 || G < 0 || dtype < ACTNN_F32 || dtype > ACTNN_BF16) return -1;
-  // min and max of every group in the activation dtype, each rounded up to 256 bytes
+  if (G && N > ((int64_t)1 << 52) / G) return -1;
+  // min and max of every group in the activation dtype, each rounded up to 256 bytes, and 256
+  // bytes for the ticket of the sensitivity / allocation kernel
   const int64_t one = (N * G * dtype_size(dtype) + 255) / 256 * 256;
-  return 2 * one;
+  return 2 * one + 256;
 }
 
 extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* scale, void* mn_out,
@@ -22,22 +26,34 @@ extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* sca
                                     uint64_t seed, uint64_t offset, actnn_stream_t stream) {
   if (N < 0 || G < 0 || group_size != kGroup) return ACTNN_ERR_SHAPE;
   if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
-  if (initial_bits < 2 || initial_bits > 8) return ACTNN_ERR_BITS;
+  if (initial_bits < 1 || initial_bits > 8) return ACTNN_ERR_BITS;
   if (N == 0 || G == 0) return ACTNN_OK;
   if (!data || !packed || !scale || !mn_out || !bits_out || !word_offsets_out || !C_out || !workspace)
     return ACTNN_ERR_NULL;
   const int64_t need = actnn_compress_mixed_workspace(N, G, dtype);
   if (workspace_bytes < need) return ACTNN_ERR_CAPACITY;
   if (!aligned(workspace, 256)) return ACTNN_ERR_ALIGN;
+  const int64_t one = (need - 256) / 2;
   void* mn = workspace;
-  void* mx = (char*)workspace + need / 2;
-  int st = actnn_minimax(data, mn, mx, N * G, group_size, dtype, stream);
+  void* mx = (char*)workspace + one;
+  unsigned* ticket = (unsigned*)((char*)workspace + 2 * one);
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool fused_alloc = range_greedy_supported(N, initial_bits);
+  // pass 1 walks the activation from its end to its start, pass 2 (the pack) from the start:
+  // what the first pass read last is what the second finds in the L2
+  int st = minimax_impl(data, mn, mx, N * G, group_size, dtype, 1, fused_alloc ? ticket : nullptr, s);
   if (st) return st;
-  st = actnn_range_sqr(mn, mx, N, G, dtype, range_factor, coeff, grad_scale, C_out, stream);
-  if (st) return st;
-  st = actnn_calc_precision(C_out, nullptr, N, initial_bits, target, bits_out, word_offsets_out, G, group_size,
-                            nullptr, 0, stream);
-  if (st) return st;
+  if (fused_alloc) {
+    st = range_greedy_impl(mn, mx, N, G, dtype, range_factor, coeff, grad_scale, C_out, ticket, initial_bits, target,
+                           bits_out, word_offsets_out, group_size, s);
+    if (st) return st;
+  } else {
+    st = actnn_range_sqr(mn, mx, N, G, dtype, range_factor, coeff, grad_scale, C_out, stream);
+    if (st) return st;
+    st = actnn_calc_precision(C_out, nullptr, N, initial_bits, target, bits_out, word_offsets_out, G, group_size,
+                              nullptr, 0, stream);
+    if (st) return st;
+  }
   return pack_mixed_impl(data, mn, mx, bits_out, word_offsets_out, packed, scale, mn_out, N, G, group_size, dtype,
                          stat_dtype, stochastic, noise, seed, offset, true, (cudaStream_t)stream);
 }
@@ -54,24 +70,25 @@ extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* sca
 // every GPU that loads the library until the process exits, and the problem size is capped.
 namespace {
 
-constexpr int64_t kStaticScratchBytes = 4 << 20;          // 4 MiB: N * G <= 1 Mi groups of 16-bit data
+// 4 MiB of min / max (N * G <= 1 Mi groups of 16-bit data) and the 256-byte ticket block
+constexpr int64_t kStaticScratchBytes = (4 << 20) + 256;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // Device address of g_static_scratch on the current device, looked up once per device.  In
 // host code the array's name is only a handle, not an address a kernel could use.
 int static_scratch_address(void** out) {
-  static void* addr[64];
-  static bool ready[64];
+  // one slot per device; the address is published with release / acquire so that a thread
+  // that sees it set also sees a complete value (the look-up itself is idempotent)
+  static std::atomic<void*> addr[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ACTNN_ERR_ARG;
-  if (!ready[dev]) {
-    void* p = nullptr;
+  void* p = addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return ACTNN_ERR_LAUNCH;
-    addr[dev] = p;
-    ready[dev] = true;
+    addr[dev].store(p, std::memory_order_release);
   }
-  *out = addr[dev];
+  *out = p;
   return ACTNN_OK;
 }
 

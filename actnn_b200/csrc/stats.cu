@@ -38,15 +38,21 @@ ACTNN_DEV void minimax256_task(const T* __restrict__ data, T* __restrict__ mn, T
   }
 }
 
+// `reverse`: walk the rows from the last to the first, so that the head of the tensor is what
+// the L2 holds when a second pass (the pack) starts reading it from the front.
+// `clear_word` (optional) is set to zero: the ticket of the kernel that follows in the stream.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-minimax256_kernel(const T* __restrict__ data, T* __restrict__ mn, T* __restrict__ mx, int64_t rows) {
+minimax256_kernel(const T* __restrict__ data, T* __restrict__ mn, T* __restrict__ mx, int64_t rows, int reverse,
+                  unsigned* __restrict__ clear_word) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const int64_t total = (rows + kMinimaxRows - 1) / kMinimaxRows;
   const int64_t whole = rows / kMinimaxRows;
-  for (int64_t task = warp; task < total; task += nwarps) {
+  if (clear_word && blockIdx.x == 0 && threadIdx.x == 0) *clear_word = 0u;
+  for (int64_t t = warp; t < total; t += nwarps) {
+    const int64_t task = reverse ? total - 1 - t : t;
     if (task < whole) minimax256_task<T, true>(data, mn, mx, rows, task * kMinimaxRows, lane);
     else minimax256_task<T, false>(data, mn, mx, rows, task * kMinimaxRows, lane);
   }
@@ -77,13 +83,15 @@ minimax_generic_kernel(const T* __restrict__ data, T* __restrict__ mn, T* __rest
 }
 
 template <typename T>
-int launch_minimax(const void* data, void* mn, void* mx, int64_t rows, int64_t cols, cudaStream_t s) {
+int launch_minimax(const void* data, void* mn, void* mx, int64_t rows, int64_t cols, cudaStream_t s,
+                   int reverse = 0, unsigned* clear_word = nullptr) {
   const int64_t cap = (int64_t)device_info().sm_count * 8;
   if (cols == kGroup) {
     const int64_t tasks = (rows + kMinimaxRows - 1) / kMinimaxRows;
     const int grid = (int)max((int64_t)1, min((tasks + 7) / 8, cap));
-    minimax256_kernel<T><<<grid, kThreads, 0, s>>>((const T*)data, (T*)mn, (T*)mx, rows);
+    minimax256_kernel<T><<<grid, kThreads, 0, s>>>((const T*)data, (T*)mn, (T*)mx, rows, reverse, clear_word);
   } else {
+    if (clear_word && cudaMemsetAsync(clear_word, 0, sizeof(unsigned), s) != cudaSuccess) return ACTNN_ERR_LAUNCH;
     const int grid = (int)max((int64_t)1, min((rows + 7) / 8, cap));
     minimax_generic_kernel<T><<<grid, kThreads, 0, s>>>((const T*)data, (T*)mn, (T*)mx, rows, cols);
   }
@@ -92,20 +100,22 @@ int launch_minimax(const void* data, void* mn, void* mx, int64_t rows, int64_t c
 
 // ---------------------------------------------------------------------------- range_sqr
 // One block per sample; fixed-shape tree reduction, hence deterministic.
+// The first kThreads threads of the block do the work (a wider block gives the same sums).
 template <typename ST>
-__global__ void __launch_bounds__(kThreads)
-range_sqr_kernel(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t G, float range_factor,
-                 float coeff, const float* __restrict__ grad_scale, float* __restrict__ C) {
+ACTNN_DEV void range_sqr_block(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t n, int64_t G,
+                               float range_factor, float coeff, const float* __restrict__ grad_scale,
+                               float* __restrict__ C) {
   __shared__ float partial[kThreads / 32];
-  const int64_t n = blockIdx.x;
-  float acc = 0.f;
-  for (int64_t g = threadIdx.x; g < G; g += kThreads) {
-    const float d = round_to<ST>(__fsub_rn(load_scalar<ST>(mx, n * G + g), load_scalar<ST>(mn, n * G + g)));
-    acc = __fmaf_rn(d, d, acc);
-  }
+  if (threadIdx.x < kThreads) {
+    float acc = 0.f;
+    for (int64_t g = threadIdx.x; g < G; g += kThreads) {
+      const float d = round_to<ST>(__fsub_rn(load_scalar<ST>(mx, n * G + g), load_scalar<ST>(mn, n * G + g)));
+      acc = __fmaf_rn(d, d, acc);
+    }
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(kFull, acc, s);
-  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(kFull, acc, s);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     float tot = 0.f;
@@ -117,6 +127,13 @@ range_sqr_kernel(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t G
     if (grad_scale) c = __fmul_rn(c, __ldg(grad_scale));
     C[n] = c;
   }
+}
+
+template <typename ST>
+__global__ void __launch_bounds__(kThreads)
+range_sqr_kernel(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t G, float range_factor,
+                 float coeff, const float* __restrict__ grad_scale, float* __restrict__ C) {
+  range_sqr_block<ST>(mn, mx, blockIdx.x, G, range_factor, coeff, grad_scale, C);
 }
 
 // ---------------------------------------------------------------------------- sample_sumsq
@@ -343,17 +360,22 @@ greedy_kernel(const float* __restrict__ C, const int32_t* __restrict__ w, int64_
 
 // Fast path for unit weights and at most THREADS samples (the per-layer call of every
 // training step): thread i owns sample i and keeps its initial_bits - 1 candidate keys in
-// registers, so nothing is recomputed and nothing but C is read.  The priority word is
-// selected first, four bits per block-wide pass (15 trial thresholds at once, one barrier
-// per pass); the (index, width) word is searched only when several candidates share the
-// boundary priority.
+// registers, so nothing is recomputed and nothing but C is read.  The K-th largest key is
+// found by radix selection, eight bits per pass over a 256-bin histogram in shared memory:
+// the bits all keys have in common are skipped first (one block-wide min / max), so that the
+// first digit already mixes exponent and mantissa bits and the histogram's atomics spread
+// over many bins.  The priority word is selected first; the (index, width) word is searched
+// only when several candidates share the boundary priority.  All THREADS threads of the block
+// must call it.
 template <int THREADS>
-__global__ void __launch_bounds__(THREADS)
-greedy_sample_kernel(const float* __restrict__ C, int N, int initial_bits, double target, GreedyCoef coef,
-                     int32_t* __restrict__ b_out, int64_t* __restrict__ word_offsets, int64_t words_per_bit) {
+ACTNN_DEV void greedy_block(float c_mine, int N, int initial_bits, double target, const GreedyCoef& coef,
+                            int32_t* __restrict__ b_out, int64_t* __restrict__ word_offsets,
+                            int64_t words_per_bit) {
   constexpr int WARPS = THREADS / 32;
   constexpr int KEYS = 8;                                      // widths initial_bits .. 2, initial_bits <= 9
-  __shared__ uint32_t part[2][WARPS][8];                       // 15 counts of 16 bits, two per word
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t sel[3];                                  // digit, remaining, size of the digit's bin
+  __shared__ uint32_t ext[2][WARPS];
   __shared__ int scan_sums[WARPS];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int per = initial_bits - 1;
@@ -364,9 +386,10 @@ greedy_sample_kernel(const float* __restrict__ C, int N, int initial_bits, doubl
 
   uint32_t key_hi[KEYS], key_lo[KEYS];                         // priority word; (index << 4) | width
 #pragma unroll
-  for (int k = 0; k < KEYS; ++k) { key_hi[k] = 0; key_lo[k] = 0; }   // below every real key
-  if (tid < N) {
-    const double c = (double)C[tid];
+  for (int k = 0; k < KEYS; ++k) { key_hi[k] = 0; key_lo[k] = 0; }
+  const bool have = tid < N;
+  if (have) {
+    const double c = (double)c_mine;
 #pragma unroll
     for (int k = 0; k < KEYS; ++k) {
       const int b = initial_bits - k;
@@ -380,27 +403,48 @@ greedy_sample_kernel(const float* __restrict__ C, int N, int initial_bits, doubl
     }
   }
 
-  // Sums the 15 packed counts over the block; returns the largest j whose count reaches
-  // `want` (0 if none).  Counts fall as j grows.
-  int buf = 0;
-  auto pick_digit = [&](uint32_t (&cnt)[8], int want) -> int {
-#pragma unroll
-    for (int w = 0; w < 8; ++w) cnt[w] = __reduce_add_sync(kFull, cnt[w]);
-    if (lane < 8) part[buf][wid][lane] = cnt[lane];
+  // One selection pass over the digit of `width` <= 8 bits at `shift` of `word[k]`, among the
+  // keys whose bits above the digit equal `prefix` (and that pass `live[k]`).  Returns the digit
+  // of the `remaining`-th largest such key and updates `remaining` to its rank inside that
+  // digit's bin.
+  uint32_t bin_size = 0;
+  auto pass = [&](const uint32_t (&word)[KEYS], const bool (&live)[KEYS], uint32_t prefix, int shift, int width,
+                  uint32_t& remaining) -> uint32_t {
+    for (int i = tid; i < 256; i += THREADS) hist[i] = 0;
     __syncthreads();
-    const int j = lane & 15, half = lane >> 4;
-    uint32_t tot = 0;
-    if (WARPS == 1) {
-      tot = half == 0 ? (part[buf][0][j >> 1] >> (16 * (j & 1))) & 0xffffu : 0u;
-    } else {
+    const uint32_t above_mask = shift + width >= 32 ? 0u : ~0u << (shift + width);
+    const uint32_t digit_mask = (1u << width) - 1u;
 #pragma unroll
-      for (int w = 0; w < WARPS / 2; ++w)
-        tot += (part[buf][half * (WARPS / 2) + w][j >> 1] >> (16 * (j & 1))) & 0xffffu;
+    for (int k = 0; k < KEYS; ++k)
+      if (live[k] && (word[k] & above_mask) == prefix) atomicAdd(&hist[(word[k] >> shift) & digit_mask], 1u);
+    __syncthreads();
+    if (wid == 0) {
+      uint32_t h[8], s = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { h[j] = hist[8 * lane + j]; s += h[j]; }
+      uint32_t suffix = s;                                     // keys in the bins of lanes >= this one
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t t = __shfl_down_sync(kFull, suffix, d);
+        if (lane + d < 32) suffix += t;
+      }
+      uint32_t acc = suffix - s;                               // keys in higher bins
+      if (acc < remaining && remaining <= suffix) {            // exactly one lane
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+          if (acc < remaining && remaining <= acc + h[j]) {
+            sel[0] = 8u * lane + j;
+            sel[1] = remaining - acc;
+            sel[2] = h[j];
+          }
+          acc += h[j];
+        }
+      }
     }
-    tot += __shfl_xor_sync(kFull, tot, 16);
-    const unsigned ok = __ballot_sync(kFull, lane >= 1 && lane < 16 && (int)tot >= want);
-    buf ^= 1;
-    return 31 - __clz((int)(ok | 1u));
+    __syncthreads();
+    remaining = sel[1];
+    bin_size = sel[2];
+    return sel[0];
   };
 
   uint32_t T_hi = 0, T_lo = 0;
@@ -409,64 +453,43 @@ greedy_sample_kernel(const float* __restrict__ C, int N, int initial_bits, doubl
   } else if (need >= total) {
     T_hi = 0; T_lo = 1;                                         // every candidate is taken
   } else {
-    for (int shift = 28; shift >= 0; shift -= 4) {
-      uint32_t cnt[8];
+    bool live[KEYS];
 #pragma unroll
-      for (int w = 0; w < 8; ++w) cnt[w] = 0;
+    for (int k = 0; k < KEYS; ++k) live[k] = have && k < per;
+    // bits shared by every key: nothing to select there
+    uint32_t lo_key = ~0u, hi_key = 0u;
 #pragma unroll
-      for (int j = 1; j < 16; ++j) {
-        const uint32_t trial = T_hi | ((uint32_t)j << shift);
-        uint32_t c = 0;
-#pragma unroll
-        for (int k = 0; k < KEYS; ++k) c += key_hi[k] >= trial ? 1u : 0u;
-        cnt[j >> 1] += c << (16 * (j & 1));
-      }
-      T_hi |= (uint32_t)pick_digit(cnt, need) << shift;
-    }
-    // candidates above the boundary priority, and those on it
-    uint32_t above = 0, on = 0;
-#pragma unroll
-    for (int k = 0; k < KEYS; ++k) {
-      above += key_hi[k] > T_hi ? 1u : 0u;
-      on += key_hi[k] == T_hi ? 1u : 0u;
-    }
-    uint32_t both = __reduce_add_sync(kFull, above | (on << 16));
-    if (lane == 0) part[buf][wid][0] = both;
+    for (int k = 0; k < KEYS; ++k)
+      if (live[k]) { lo_key = min(lo_key, key_hi[k]); hi_key = max(hi_key, key_hi[k]); }
+    lo_key = __reduce_min_sync(kFull, lo_key);
+    hi_key = __reduce_max_sync(kFull, hi_key);
+    if (lane == 0) { ext[0][wid] = lo_key; ext[1][wid] = hi_key; }
     __syncthreads();
-    both = 0;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) both += part[buf][w][0];
-    buf ^= 1;
-    const int n_above = (int)(both & 0xffffu), n_on = (int)(both >> 16);
-    const int need_lo = need - n_above;                         // 1 .. n_on
-    if (need_lo >= n_on) {
+    for (int w = 0; w < WARPS; ++w) { lo_key = min(lo_key, ext[0][w]); hi_key = max(hi_key, ext[1][w]); }
+    const int varying = 32 - __clz((int)(lo_key ^ hi_key));      // low bits in which keys differ (0..32)
+    uint32_t remaining = (uint32_t)need;
+    uint32_t prefix = varying >= 32 ? 0u : (hi_key >> varying) << varying;
+    for (int top = varying; top > 0; top -= 8) {
+      const int width = top >= 8 ? 8 : top, shift = top - width;
+      prefix |= pass(key_hi, live, prefix, shift, width, remaining) << shift;
+    }
+    if (varying == 0) bin_size = (uint32_t)total;               // every key has the same priority
+    T_hi = prefix;
+    if (remaining >= bin_size) {
       T_lo = 0;                                                 // the whole tie is taken
     } else {
-      int low_bits = 4;
-      while ((1 << (low_bits - 4)) < N) ++low_bits;
-      low_bits = (low_bits + 3) & ~3;
-      uint32_t tied[KEYS];
+      bool tied[KEYS];
 #pragma unroll
-      for (int k = 0; k < KEYS; ++k) tied[k] = key_hi[k] == T_hi ? key_lo[k] : 0u;
-      for (int shift = low_bits - 4; shift >= 0; shift -= 4) {
-        uint32_t cnt[8];
-#pragma unroll
-        for (int w = 0; w < 8; ++w) cnt[w] = 0;
-#pragma unroll
-        for (int j = 1; j < 16; ++j) {
-          const uint32_t trial = T_lo | ((uint32_t)j << shift);
-          uint32_t c = 0;
-#pragma unroll
-          for (int k = 0; k < KEYS; ++k) c += tied[k] >= trial ? 1u : 0u;
-          cnt[j >> 1] += c << (16 * (j & 1));
-        }
-        T_lo |= (uint32_t)pick_digit(cnt, need_lo) << shift;
-      }
+      for (int k = 0; k < KEYS; ++k) tied[k] = live[k] && key_hi[k] == T_hi;
+      const uint32_t d1 = pass(key_lo, tied, 0u, 8, 8, remaining);      // (index << 4 | width) < 2^14
+      const uint32_t d0 = pass(key_lo, tied, d1 << 8, 0, 8, remaining);
+      T_lo = (d1 << 8) | d0;
     }
   }
 
   int b = 0;
-  if (tid < N) {
+  if (have) {
     b = initial_bits;
 #pragma unroll
     for (int k = 0; k < KEYS; ++k)
@@ -490,9 +513,41 @@ greedy_sample_kernel(const float* __restrict__ C, int N, int initial_bits, doubl
       before += w < wid ? v : 0;
       block_total += v;
     }
-    if (tid < N) word_offsets[tid] = (int64_t)(before + incl - b) * words_per_bit;
+    if (have) word_offsets[tid] = (int64_t)(before + incl - b) * words_per_bit;
     if (tid == 0) word_offsets[N] = (int64_t)block_total * words_per_bit;
   }
+}
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+greedy_sample_kernel(const float* __restrict__ C, int N, int initial_bits, double target, GreedyCoef coef,
+                     int32_t* __restrict__ b_out, int64_t* __restrict__ word_offsets, int64_t words_per_bit) {
+  const float c = (int)threadIdx.x < N ? C[threadIdx.x] : 0.f;
+  greedy_block<THREADS>(c, N, initial_bits, target, coef, b_out, word_offsets, words_per_bit);
+}
+
+// Sensitivities and bit allocation of one layer in ONE launch: block n computes C[n]; the
+// block that takes the last ticket (no block waits for another) then runs the greedy over all
+// N sensitivities and leaves the ticket at zero for the next call on the same workspace.
+template <typename ST, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+range_greedy_kernel(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t G, float range_factor,
+                    float coeff, const float* __restrict__ grad_scale, float* __restrict__ C, unsigned* ticket,
+                    int N, int initial_bits, double target, GreedyCoef coef, int32_t* __restrict__ b_out,
+                    int64_t* __restrict__ word_offsets, int64_t words_per_bit) {
+  static_assert(THREADS >= kThreads, "the range reduction uses kThreads threads");
+  __shared__ bool last;
+  range_sqr_block<ST>(mn, mx, blockIdx.x, G, range_factor, coeff, grad_scale, C);
+  if (threadIdx.x == 0) {
+    __threadfence();                                           // C[n] before the ticket
+    last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  const float c = (int)threadIdx.x < N ? __ldcg(C + threadIdx.x) : 0.f;
+  if (threadIdx.x == 0) *ticket = 0u;
+  greedy_block<THREADS>(c, N, initial_bits, target, coef, b_out, word_offsets, words_per_bit);
 }
 
 // Large or weighted problems (the once-per-step allocation over layers x samples) with a
@@ -599,20 +654,60 @@ greedy_ws_finish_kernel(const float* __restrict__ C, const int32_t* __restrict__
 
 using namespace actnn;
 
-extern "C" int actnn_minimax(const void* data, void* mn, void* mx, int64_t rows, int64_t cols, int dtype,
-                             actnn_stream_t stream) {
+static GreedyCoef make_greedy_coef() {
+  const GreedyCoef coef = make_greedy_coef();
+  return coef;
+}
+
+namespace actnn {
+int minimax_impl(const void* data, void* mn, void* mx, int64_t rows, int64_t cols, int dtype, int reverse,
+                 unsigned* clear_word, cudaStream_t s) {
   if (rows < 0 || cols <= 32 || cols % 32 != 0) return ACTNN_ERR_SHAPE;    // minimax_cuda_kernel.cu:80
   if (rows > ((int64_t)1 << 52) / cols) return ACTNN_ERR_SHAPE;
   if (rows == 0) return ACTNN_OK;
   if (!data || !mn || !mx) return ACTNN_ERR_NULL;
   if (cols == kGroup && !aligned(data, dtype == ACTNN_F32 ? 32 : 16)) return ACTNN_ERR_ALIGN;
-  cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
-    case ACTNN_F32: return launch_minimax<float>(data, mn, mx, rows, cols, s);
-    case ACTNN_F16: return launch_minimax<__half>(data, mn, mx, rows, cols, s);
-    case ACTNN_BF16: return launch_minimax<__nv_bfloat16>(data, mn, mx, rows, cols, s);
+    case ACTNN_F32: return launch_minimax<float>(data, mn, mx, rows, cols, s, reverse, clear_word);
+    case ACTNN_F16: return launch_minimax<__half>(data, mn, mx, rows, cols, s, reverse, clear_word);
+    case ACTNN_BF16: return launch_minimax<__nv_bfloat16>(data, mn, mx, rows, cols, s, reverse, clear_word);
     default: return ACTNN_ERR_DTYPE;
   }
+}
+
+bool range_greedy_supported(int64_t N, int initial_bits) { return N >= 1 && N <= 1024 && initial_bits >= 1 && initial_bits <= 9; }
+
+int range_greedy_impl(const void* mn, const void* mx, int64_t N, int64_t G, int stat_dtype, float range_factor,
+                      float coeff, const float* grad_scale, float* C, unsigned* ticket, int initial_bits,
+                      double target, int32_t* b_out, int64_t* word_offsets, int64_t group_size, cudaStream_t s) {
+  if (!range_greedy_supported(N, initial_bits)) return ACTNN_ERR_SHAPE;
+  if (!mn || !mx || !C || !ticket || !b_out || !word_offsets) return ACTNN_ERR_NULL;
+  if (!(target == target)) return ACTNN_ERR_ARG;
+  const GreedyCoef coef = make_greedy_coef();
+  const int64_t wpb = G * group_size / 32;
+  const int n = (int)N;
+#define ACTNN_RG(ST, T)                                                                                     \
+  range_greedy_kernel<ST, T><<<n, T, 0, s>>>((const ST*)mn, (const ST*)mx, G, range_factor, coeff, grad_scale, C, \
+                                             ticket, n, initial_bits, target, coef, b_out, word_offsets, wpb)
+#define ACTNN_RG_N(ST)                                     \
+  if (n <= 256) ACTNN_RG(ST, 256);                         \
+  else if (n <= 512) ACTNN_RG(ST, 512);                    \
+  else ACTNN_RG(ST, 1024)
+  switch (stat_dtype) {
+    case ACTNN_F32: ACTNN_RG_N(float); break;
+    case ACTNN_F16: ACTNN_RG_N(__half); break;
+    case ACTNN_BF16: ACTNN_RG_N(__nv_bfloat16); break;
+    default: return ACTNN_ERR_DTYPE;
+  }
+#undef ACTNN_RG_N
+#undef ACTNN_RG
+  return check_launch();
+}
+}  // namespace actnn
+
+extern "C" int actnn_minimax(const void* data, void* mn, void* mx, int64_t rows, int64_t cols, int dtype,
+                             actnn_stream_t stream) {
+  return minimax_impl(data, mn, mx, rows, cols, dtype, 0, nullptr, (cudaStream_t)stream);
 }
 
 extern "C" int actnn_range_sqr(const void* mn, const void* mx, int64_t N, int64_t G, int stat_dtype,
@@ -646,7 +741,7 @@ extern "C" int64_t actnn_calc_precision_workspace(void) { return 256; }
 extern "C" int actnn_calc_precision(const float* C, const int32_t* w, int64_t N, int initial_bits, double target,
                                     int32_t* b_out, int64_t* word_offsets, int64_t G, int64_t group_size,
                                     void* workspace, int64_t workspace_bytes, actnn_stream_t stream) {
-  if (initial_bits < 2 || initial_bits > 15) return ACTNN_ERR_BITS;
+  if (initial_bits < 1 || initial_bits > 15) return ACTNN_ERR_BITS;   // 1: nothing to remove, all ones
   if (N < 0 || N > (1 << 20)) return ACTNN_ERR_SHAPE;
   if (word_offsets && (G < 0 || group_size <= 0 || group_size % 32 != 0)) return ACTNN_ERR_SHAPE;
   if (!(target == target)) return ACTNN_ERR_ARG;
@@ -656,14 +751,7 @@ extern "C" int actnn_calc_precision(const float* C, const int32_t* w, int64_t N,
     return ACTNN_OK;
   }
   if (!C || !b_out) return ACTNN_ERR_NULL;
-  GreedyCoef coef;
-  for (int b = 0; b < 16; ++b) {
-    if (b < 2) { coef.c[b] = 0.0; continue; }
-    // the reference's get_obj (calc_precision.cc:24-28), in integers wide enough not to wrap
-    const int64_t c1 = (((int64_t)1 << b) - 1) * (((int64_t)1 << b) - 1);
-    const int64_t c2 = (((int64_t)1 << (b - 1)) - 1) * (((int64_t)1 << (b - 1)) - 1);
-    coef.c[b] = 1.0 / (double)c1 - 1.0 / (double)c2;
-  }
+  const GreedyCoef coef = make_greedy_coef();
   const int64_t wpb = word_offsets ? G * group_size / 32 : 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t candidates = N * (initial_bits - 1);

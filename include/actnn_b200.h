@@ -159,7 +159,7 @@ int actnn_sample_sumsq(const void* grad, float* out, int64_t N, int64_t F, int d
  * actnn/actnn/cpp_extension/calc_precision.cc:9-50 (a CPU priority queue there; here a
  * weighted radix select over the (initial_bits-1)*N candidate decrements, identical
  * results including tie-breaks).  C[N] float32, w[N] int32 or NULL (all ones),
- * b_out[N] int32, every entry starting from `initial_bits` (2..15).  If word_offsets is
+ * b_out[N] int32, every entry starting from `initial_bits` (1..15; 1 leaves nothing to remove).  If word_offsets is
  * not NULL it receives what actnn_bits_prefix would (needs G, group_size).
  * N <= 2^20.  Small unit-weight problems run in one thread block.  `workspace` (optional,
  * actnn_calc_precision_workspace() bytes, 8-byte aligned, contents unspecified before and
@@ -198,7 +198,7 @@ int actnn_compress_mixed(const void* data, int32_t* packed, void* scale, void* m
  * framework that owns all device memory and offers no allocator, or a job whose device
  * memory was planned out in advance so that one more cudaMalloc may fail or upset the plan.
  * Same arguments and results as actnn_compress_mixed without `workspace`: the per-group
- * min / max go to an array of actnn_compress_mixed_static_capacity() bytes (4 MiB) that is
+ * min / max go to an array of actnn_compress_mixed_static_capacity() bytes (4 MiB + 256) that is
  * part of the library image, i.e. resident on every GPU that loads the library until the
  * process ends.  Limits and rules:
  *   - actnn_compress_mixed_workspace(N, G, dtype) must not exceed the capacity (N*G up to
@@ -317,6 +317,15 @@ int actnn_batch_norm_backward_elemt(const void* x, const void* grad_out, const f
  * a warp whose wait runs out stops and leaves its outputs unwritten.  Zero in every
  * healthy run; reading it synchronises with the device.  No counterpart in the reference. */
 int actnn_bulk_wait_failures(uint32_t* count);
+
+/* ------------------------------------------------------------------------------------
+ * How many four-group bundles actnn_pack_mixed / actnn_compress_mixed met, on the current
+ * device since the library was loaded, whose per-sample width was outside 1..8: nothing is
+ * written for such a bundle (the widths live on the device, so the entry point itself cannot
+ * refuse them without a synchronisation).  Zero in every healthy run; reading it synchronises
+ * with the device.  The reference accepts any width its caller passes
+ * (quantization_cuda_kernel.cu:94-142) and has no such check. */
+int actnn_bad_width_bundles(uint32_t* count);
 
 /* ------------------------------------------------------------------------------------
  * The rounding noise the pack kernels draw for (seed, offset) when `noise == NULL`,

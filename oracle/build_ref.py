@@ -21,7 +21,7 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 MOD_NAME = "ref_calc_precision"
-DEFAULT_REFERENCE = os.environ.get("ACTNN_REFERENCE_ROOT", "/root/reference")
+DEFAULT_REFERENCE = os.environ.get("ACTNN_REFERENCE_ROOT")      # no built-in location: set it, or pass a path
 
 
 def so_path() -> str:
@@ -30,8 +30,10 @@ def so_path() -> str:
 
 def build(reference_root: str = DEFAULT_REFERENCE, force: bool = False) -> str | None:
     """Build if the reference source is present; return the .so path (or None)."""
-    src = os.path.join(reference_root, "actnn", "actnn", "cpp_extension", "calc_precision.cc")
     out = so_path()
+    if not reference_root:
+        return out if os.path.exists(out) else None
+    src = os.path.join(reference_root, "actnn", "actnn", "cpp_extension", "calc_precision.cc")
     if not os.path.exists(src):
         return out if os.path.exists(out) else None
     if os.path.exists(out) and not force and os.path.getmtime(out) >= os.path.getmtime(src):

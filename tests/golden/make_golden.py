@@ -39,7 +39,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REFERENCE = os.environ.get("ACTNN_REFERENCE_ROOT", "/root/reference")
+REFERENCE = os.environ.get("ACTNN_REFERENCE_ROOT")
+if not REFERENCE:
+    raise SystemExit("set ACTNN_REFERENCE_ROOT to the root of a checkout of the reference")
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
 
 
@@ -203,6 +205,46 @@ def main():
         out[f"g{t}__b"] = b.numpy().astype(np.int8)
     np.savez_compressed(os.path.join(HERE, "calc_precision.npz"), **out)
     print("calc_precision: 40 cases")
+
+    # ---- 4. per-layer re-allocation (qscheme.py:96-128, qbnscheme.py:54-60) ----
+    # Both branches of QScheme.allocate_perlayer: the joint allocation over layers x samples
+    # (group bits != initial bits: each layer gets the mean width of its samples) and the
+    # one-width-per-layer allocation (group bits == initial bits), then the batch-norm schemes
+    # that copy the width of the conv / linear layer in front of them.
+    out = {}
+    config.perlayer = True
+    case = 0
+    for group_bits, initial_bits, L, N in ((2, 8, 4, 6), (2, 8, 7, 16), (3, 8, 5, 8), (4, 4, 5, 6), (8, 8, 3, 4),
+                                           (2, 2, 4, 5)):
+        QScheme.layers.clear()
+        QBNScheme.layers.clear()
+        config.activation_compression_bits = [group_bits]
+        config.initial_bits = initial_bits
+        torch.manual_seed(400 + case)
+        dims = torch.randint(1, 40, (L,)) * 256
+        Cs = torch.exp(torch.randn(L, N) * 1.5) * torch.exp(torch.randn(L, 1))
+        follows = []
+        for i in range(L):
+            layer = QScheme(None)
+            layer.C = Cs[i].clone()
+            layer.dim = int(dims[i])
+            if i % 2 == 0:
+                bn = QBNScheme()                               # prev_linear = the layer just made
+                follows.append(i)
+        QScheme.allocate_perlayer()
+        QBNScheme.allocate_perlayer()
+        key = f"p{case}"
+        out[f"{key}__C"] = Cs.numpy()
+        out[f"{key}__dims"] = dims.numpy().astype(np.int64)
+        out[f"{key}__cfg"] = np.array([group_bits, initial_bits], dtype=np.int64)
+        out[f"{key}__bits"] = np.array([float(layer.bits) for layer in QScheme.layers], dtype=np.float32)
+        out[f"{key}__bn_follows"] = np.array(follows, dtype=np.int64)
+        out[f"{key}__bn_bits"] = np.array([float(bn.bits) for bn in QBNScheme.layers], dtype=np.float32)
+        case += 1
+    QScheme.layers.clear()
+    QBNScheme.layers.clear()
+    np.savez_compressed(os.path.join(HERE, "perlayer.npz"), **out)
+    print("perlayer:", case, "cases")
 
 
 if __name__ == "__main__":

@@ -72,7 +72,7 @@ def test_host_side_validation_needs_no_gpu(lib):
     assert lib.actnn_unpack_mixed(None, None, None, None, None, None, 2, 1, 256, 2, 0, None) == DTYPE
     assert lib.actnn_unpack_single(None, 8, None, None, None, 2, 1, 256, 0, 2, None) == NULL
     # bit allocation
-    assert lib.actnn_calc_precision(None, None, 4, 1, 8.0, None, None, 0, 256, None, 0, None) == BITS
+    assert lib.actnn_calc_precision(None, None, 4, 0, 8.0, None, None, 0, 256, None, 0, None) == BITS
     assert lib.actnn_calc_precision(None, None, 4, 8, float("nan"), None, None, 0, 256, None, 0, None) == ARG
     assert lib.actnn_calc_precision(None, None, 4, 8, 8.0, None, None, 0, 256, None, 0, None) == NULL
     assert lib.actnn_bits_prefix(None, 4, 1, 100, None, None) == NULL
@@ -85,8 +85,8 @@ def test_host_side_validation_needs_no_gpu(lib):
     assert lib.actnn_max_pool2d_forward(None, None, None, 1, 1, 8, 8, 2, 2, 2, 2, 0, 0, 1, 1, 0, None) == NULL
     assert lib.actnn_noise_fill(None, 8, 0, 1, 2, None) == NULL
     # one-call adaptive compress: workspace size and capacity check
-    assert lib.actnn_compress_mixed_workspace(4, 3, 1) == 2 * 256
-    assert lib.actnn_compress_mixed_workspace(512, 784, 0) == 2 * 512 * 784 * 4
+    assert lib.actnn_compress_mixed_workspace(4, 3, 1) == 2 * 256 + 256
+    assert lib.actnn_compress_mixed_workspace(512, 784, 0) == 2 * 512 * 784 * 4 + 256
     assert lib.actnn_compress_mixed_workspace(-1, 3, 1) == -1
     args = [256] * 8 + [8, 4, 3, 256, 1, 1, 1.0, 1.0, None, 8, 8.0, 1, None, 0, 0, None]
     assert lib.actnn_compress_mixed(*args) == 8                      # ACTNN_ERR_CAPACITY: workspace too small

@@ -35,10 +35,11 @@ def test_uniform_2bit_float32_round_trip_64x64x56x56(ext):
     assert packed.numel() == O.single_total_bytes(bits, N, G, 256)
     noise = ext.q.noise_fill(x.numel(), torch.float32, "cuda", seed, offset).view(N, G, 256)
 
-    # (1) the first and the last block of 8/bits samples against the oracle, bit for bit
+    # (1) the first, a middle and the last block of 8/bits samples against the oracle, bit for bit
+    # (the middle one lies where the persistent grid has wrapped around many times)
     wpt = 8 // bits
     block_bytes = G * 256
-    for no in (0, N // wpt - 1):
+    for no in (0, (N // wpt) // 2 + 1, N // wpt - 1):
         rows = slice(no * wpt, (no + 1) * wpt)
         xs = x[rows].cpu()
         omn, omx = O.group_minimax(xs)
@@ -100,8 +101,9 @@ def test_adaptive_bfloat16_512x256x28x28(ext):
     assert packed.numel() == 2 * N * G * 256 // 32
     noise = ext.q.noise_fill(x.numel(), dt, "cuda", seed, offset).view(N, G, 256)
 
-    # (1) two samples from each end against the oracle, word for word
-    for rows in (slice(0, 2), slice(N - 2, N)):
+    # (1) two samples from each end and two from the middle (where the persistent grid has
+    # wrapped around many times and tasks straddle sample boundaries) against the oracle, word for word
+    for rows in (slice(0, 2), slice(N // 2 + 1, N // 2 + 3), slice(N - 2, N)):
         xs, ws = x[rows].cpu(), w_cpu[rows]
         omn, omx = O.group_minimax(xs)
         codes, oscale = O.quantize(xs, ws, omn, omx, noise[rows].cpu())

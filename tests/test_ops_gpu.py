@@ -201,3 +201,55 @@ def test_autocast_conv_runs_in_half(actnn):
     assert y.dtype == torch.float16
     y.float().sum().backward()
     assert x.grad is not None and conv.weight.grad is not None and conv.weight.grad.dtype == torch.float32
+
+
+# ------------------------------------------------------------------------------ per-layer widths
+PERLAYER = load_cases("perlayer")
+
+
+@pytest.mark.parametrize("case", sorted(PERLAYER))
+def test_allocate_perlayer_matches_the_reference(actnn, case):
+    """``QScheme.allocate_perlayer`` / ``QBNScheme.allocate_perlayer`` against the widths the
+    reference's own code produced for the same sensitivities (qscheme.py:96-128,
+    qbnscheme.py:54-60): the joint allocation over layers x samples, the one-width-per-layer
+    branch (group bits == initial bits) and the batch norms that follow their conv layer."""
+    f = PERLAYER[case]
+    group_bits, initial_bits = (int(v) for v in f["cfg"])
+    actnn.config.perlayer = True
+    actnn.config.activation_compression_bits = [group_bits]
+    actnn.config.initial_bits = initial_bits
+    actnn.QScheme.layers.clear()
+    actnn.QBNScheme.layers.clear()
+    follows = set(int(i) for i in f["bn_follows"])
+    bns = []
+    for i in range(f["C"].shape[0]):
+        layer = actnn.QScheme(None)
+        layer.C = torch.from_numpy(f["C"][i]).cuda()
+        layer.dim = int(f["dims"][i])
+        if i in follows:
+            bns.append(actnn.QBNScheme())
+    actnn.QScheme.allocate_perlayer()
+    actnn.QBNScheme.allocate_perlayer()
+    got = np.array([float(layer.bits) for layer in actnn.QScheme.layers], dtype=np.float32)
+    assert np.array_equal(got, f["bits"])
+    assert np.array_equal(np.array([float(b.bits) for b in bns], dtype=np.float32), f["bn_bits"])
+    if group_bits == initial_bits:                       # that branch also moves the starting width
+        assert [int(layer.initial_bits) for layer in actnn.QScheme.layers] == [int(b) for b in f["bits"]]
+    actnn.QScheme.layers.clear()
+    actnn.QBNScheme.layers.clear()
+
+
+def test_a_layer_allocated_one_bit_still_compresses(actnn):
+    """The one-width-per-layer branch can hand a layer 1 bit as its STARTING width
+    (``layer.initial_bits = b[i]``, qscheme.py:111); the reference's greedy then returns all
+    ones.  The compress must accept that instead of failing in the middle of training."""
+    actnn.config.activation_compression_bits = [1]
+    actnn.config.initial_bits = 1
+    layer = actnn.QScheme(None)
+    x = torch.randn(6, 8, 16, 16, device="cuda")
+    q = actnn.ops.quantize_activation(x, layer)
+    assert q[1].tolist() == [1] * 6
+    y = actnn.ops.dequantize_activation(q, x.shape, x.dtype)
+    assert torch.isfinite(y).all()
+    groups, b, _, _ = layer.compute_quantization_bits(x)
+    assert b.tolist() == [1] * 6

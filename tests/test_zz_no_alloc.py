@@ -51,11 +51,49 @@ def test_static_scratch_variant_matches_the_workspace_variant_twice_in_a_row(cud
         assert int(got["bits"].sum()) == 2 * shape[0]
 
 
+def test_static_scratch_variant_allocates_nothing_and_takes_the_largest_size(cuda_device):
+    """The largest problem that fits (1 Mi groups of float16: exactly the capacity), and the
+    property the entry point exists for: across a call neither the driver's free memory nor
+    torch's count of device allocations moves."""
+    from actnn_b200 import _lib
+    lib = _lib.load()
+    n, g = 1024, 1024
+    assert lib.actnn_compress_mixed_workspace(n, g, 1) == lib.actnn_compress_mixed_static_capacity()
+    gen = torch.Generator().manual_seed(7)
+    x = torch.randn(n, g, 256, generator=gen).to(torch.float16).to(cuda_device)
+    ref = _run(lib, _lib, x, static=False, seed=5)
+    _run(lib, _lib, x, static=True, seed=5)              # first call on the device: looks the array up
+    total = 2 * n
+    out = {
+        "packed": torch.zeros(total * g * 256 // 32, dtype=torch.int32, device=cuda_device),
+        "scale": torch.zeros(n, g, 1, dtype=x.dtype, device=cuda_device),
+        "mn": torch.zeros(n, g, 1, dtype=x.dtype, device=cuda_device),
+        "bits": torch.zeros(n, dtype=torch.int32, device=cuda_device),
+        "offsets": torch.zeros(n + 1, dtype=torch.int64, device=cuda_device),
+        "C": torch.zeros(n, dtype=torch.float32, device=cuda_device),
+    }
+    dt = _lib.dtype_id(x.dtype)
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    allocs_before = torch.cuda.memory_stats()["num_device_alloc"]
+    st = lib.actnn_compress_mixed_static(
+        x.data_ptr(), out["packed"].data_ptr(), out["scale"].data_ptr(), out["mn"].data_ptr(), out["bits"].data_ptr(),
+        out["offsets"].data_ptr(), out["C"].data_ptr(), n, g, 256, dt, dt, 256 / 64.0, 9 / 4, None, 8, float(total), 1,
+        None, 5, 8, stream)
+    torch.cuda.synchronize()
+    assert st == 0
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_stats()["num_device_alloc"] == allocs_before
+    for key in ref:
+        assert torch.equal(ref[key], out[key]), key
+
+
 def test_static_scratch_variant_rejects_what_does_not_fit(cuda_device):
     from actnn_b200 import _lib
     lib = _lib.load()
     cap = lib.actnn_compress_mixed_static_capacity()
-    assert cap == 4 << 20
+    assert cap == (4 << 20) + 256                     # 4 MiB of min / max and the ticket block
     n, g = 2048, 1024                                 # 2 Mi groups of float16: 8 MiB of min / max
     assert lib.actnn_compress_mixed_workspace(n, g, 1) > cap
     dummy = torch.zeros(64, device=cuda_device)
