@@ -70,7 +70,13 @@ def pack_mixed_precision(data, min, max, bits, stochastic, *, noise=None, philox
     if word_offsets is None:
         word_offsets = bits_prefix(bits, g, gs)
     if total_bits is None:
-        words = int(word_offsets[-1].item())
+        # the reference-style call: one host read for the size (quantization_cuda_kernel.cu:97-98);
+        # the same read checks the widths, which the kernels cannot refuse on their own
+        lo, hi, words = (int(v) for v in torch.stack([bits.min().long(), bits.max().long(),
+                                                      word_offsets[-1]]).tolist()) if n else (1, 1, 0)
+        if lo < 1 or hi > 8:
+            raise RuntimeError("pack_mixed_precision: bit widths must lie in 1..8, got %d..%d "
+                               "(unsupported bit width)" % (lo, hi))
     else:
         words = (int(total_bits) * g * gs + 31) // 32
     sdt = _stat_dtype(data.dtype, stat_dtype)

@@ -655,7 +655,14 @@ greedy_ws_finish_kernel(const float* __restrict__ C, const int32_t* __restrict__
 using namespace actnn;
 
 static GreedyCoef make_greedy_coef() {
-  const GreedyCoef coef = make_greedy_coef();
+  GreedyCoef coef;
+  for (int b = 0; b < 16; ++b) {
+    if (b < 2) { coef.c[b] = 0.0; continue; }
+    // the reference's get_obj (calc_precision.cc:24-28), in integers wide enough not to wrap
+    const int64_t c1 = (((int64_t)1 << b) - 1) * (((int64_t)1 << b) - 1);
+    const int64_t c2 = (((int64_t)1 << (b - 1)) - 1) * (((int64_t)1 << (b - 1)) - 1);
+    coef.c[b] = 1.0 / (double)c1 - 1.0 / (double)c2;
+  }
   return coef;
 }
 

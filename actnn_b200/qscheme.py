@@ -169,7 +169,9 @@ class QScheme(object):
                                  device=device).repeat_interleave(N).contiguous()
                 total = float(sum(layer.dim for layer in layers) * N * group_bits)
                 b, _ = ext_calc_precision.allocate_bits(C, config.initial_bits, total, w)
-                means = b.view(L, N).float().mean(dim=1).cpu()        # the one host read per step
+                # the one host read per step.  Integer sums are exact on any device; the division
+                # is done on the host in float32 like the reference's ``bs.float().mean()``
+                means = b.view(L, N).sum(dim=1).cpu().float() / N
                 for i, layer in enumerate(layers):
                     layer.bits = means[i]
 

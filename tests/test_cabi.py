@@ -126,3 +126,16 @@ def test_package_api_surface():
         assert callable(getattr(quantization, fn))
     assert callable(minimax.minimax) and callable(calc_precision.calc_precision)
     assert callable(backward_func.cudnn_convolution_backward)
+
+
+def test_host_code_past_validation_returns_without_a_gpu(lib):
+    """On a machine without a GPU the entry points get past their argument checks, fail to
+    launch and say so; they must not spin or block in host code."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("would launch kernels on made-up pointers")
+    LAUNCH = 7
+    assert lib.actnn_calc_precision(256, None, 4, 8, 8.0, 256, None, 0, 256, None, 0, None) == LAUNCH
+    assert lib.actnn_minimax(256, 256, 256, 8, 256, 1, None) == LAUNCH
+    args = [256] * 8 + [1 << 20, 4, 32, 256, 1, 1, 1.0, 1.0, None, 8, 8.0, 1, None, 0, 0, None]
+    assert lib.actnn_compress_mixed(*args) == LAUNCH

@@ -2,9 +2,13 @@
 ``torch.nn.SyncBatchNorm`` on the same shards, with UNEQUAL per-rank batch sizes so that the
 per-rank counts in the gathered ``[mean, invstd, count]`` message and in the backward matter.
 
-Needs two GPUs: each rank is a child process on its own device, NCCL between them (NVLS off).
-On a one-GPU machine the test is skipped; the single-rank path is covered in
-``test_batch_norm_gpu.py``.
+Needs two GPUs that may talk to each other: each rank is a child process on its own device,
+NCCL between them (NVLS off), every wait bounded (a process-group timeout of one minute, a
+join timeout of three).  It runs only when ``ACTNN_TEST_GPUS`` is set to 2 or more (and that
+many devices are visible): on a one-GPU allotment of a larger machine the other devices may
+be visible without being usable.  The single-rank path is covered in ``test_batch_norm_gpu.py``.
+
+    ACTNN_TEST_GPUS=2 python -m pytest tests/test_sync_bn_multi_gpu.py -m gpu
 """
 import os
 import sys
@@ -26,7 +30,9 @@ def _worker(rank, world, port, result_dir):
 
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=60))
     try:
         actnn.config.__dict__.update(QuantizationConfig().__dict__)
         actnn.set_optimization_level("L0")                     # exact activations: only the sync logic differs
@@ -73,11 +79,18 @@ def _worker(rank, world, port, result_dir):
 
 
 def test_sync_batch_norm_two_ranks_unequal_batches(tmp_path):
+    if int(os.environ.get("ACTNN_TEST_GPUS", "1")) < 2:
+        pytest.skip("set ACTNN_TEST_GPUS=2 on a machine with two usable GPUs")
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     port = 29600 + os.getpid() % 300
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    ctx = mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=False)
+    if not ctx.join(timeout=180):
+        for proc in ctx.processes:                      # exactly the children started above
+            if proc.is_alive():
+                proc.kill()
+        pytest.fail("the two ranks did not finish within three minutes")
     for rank in range(2):
         ok, same, worst = open(os.path.join(str(tmp_path), "rank%d.txt" % rank)).read().split()
         assert ok == "1", "rank %d differs from torch.nn.SyncBatchNorm (worst relative error %s)" % (rank, worst)
