@@ -13,7 +13,8 @@ from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_uint64, c_void
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libactnn_b200.so")
+# ACTNN_B200_LIB: load another build of the library (same ABI) instead of the in-tree one
+LIB_PATH = os.environ.get("ACTNN_B200_LIB") or os.path.join(_HERE, "csrc", "libactnn_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 _DTYPE_ID = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}

