@@ -34,6 +34,9 @@ SIGNATURES = {
                              _U, _U, _P],
     "actnn_compress_mixed_static": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _F, _F, _P, _I, _D, _I, _P, _U,
                                     _U, _P],
+    "actnn_compress_mixed_prestat": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _F, _F, _P, _I, _D, _I,
+                                     _P, _U, _U, _P],
+    "actnn_batch_norm_stats_minimax": [_P] * 9 + [_L, _L, _L, _D, _D, _I, _P, _L, _P],
     "actnn_range_sqr": [_P, _P, _L, _L, _I, _F, _F, _P, _P, _P],
     "actnn_sample_sumsq": [_P, _P, _L, _L, _I, _P],
     "actnn_calc_precision": [_P, _P, _L, _I, _D, _P, _P, _L, _L, _P, _L, _P],
@@ -81,6 +84,8 @@ def load() -> ctypes.CDLL:
         lib.actnn_calc_precision_workspace.restype = c_int64
         lib.actnn_batch_norm_workspace.argtypes = [c_int64, c_int64, c_int64]
         lib.actnn_batch_norm_workspace.restype = c_int64
+        lib.actnn_batch_norm_stats_minimax_workspace.argtypes = [c_int64, c_int64, c_int64]
+        lib.actnn_batch_norm_stats_minimax_workspace.restype = c_int64
         lib.actnn_compress_mixed_static_capacity.argtypes = []
         lib.actnn_compress_mixed_static_capacity.restype = c_int64
         _lib = lib
@@ -107,12 +112,35 @@ def ptr(t) -> int:
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
+def stream_of_index(idx: int) -> int:
+    if _raw_stream is not None:
+        return _raw_stream(idx)
+    return torch.cuda.current_stream(idx).cuda_stream
+
+
 def stream_of(t: torch.Tensor) -> int:
     """The raw ``cudaStream_t`` of torch's current stream on the tensor's device."""
     if _raw_stream is not None:
         idx = t.device.index
         return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+_scratch = {}
+
+
+def scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A uint8 scratch buffer of at least ``nbytes`` for kernels launched on the CURRENT stream
+    of ``device``.  One grow-only buffer per (device, stream): the kernels that share it run in
+    stream order, so the next user only starts when the previous one is done.  Saves a trip to
+    the allocator in every layer of every step."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, stream_of_index(idx))
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(int(nbytes), 1 << 20)
+        buf = _scratch[key] = torch.empty((size + 255) // 256 * 256, dtype=torch.uint8, device=device)
+    return buf
 
 
 _fns = {}

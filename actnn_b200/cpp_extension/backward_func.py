@@ -71,8 +71,10 @@ def _bn_dims(input):
 
 
 def _bn_workspace(N, C, HW, device):
+    """Scratch of the batch-norm kernels (they clear what must start at zero themselves), taken
+    from the per-stream scratch buffer instead of the allocator."""
     nbytes = _lib.load().actnn_batch_norm_workspace(N, C, HW)
-    return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device), nbytes
+    return _lib.scratch(device, max(nbytes, 16)), nbytes
 
 
 def cudnn_batch_norm(input, weight, bias, running_mean, running_var, training, exponential_average_factor,
@@ -144,12 +146,48 @@ def batch_norm_stats(input, eps, out=None):
     return flat[:C], flat[C:2 * C]
 
 
+def batch_norm_stats_minimax(input, weight, bias, running_mean, running_var, momentum, eps, out=None):
+    """Batch-norm statistics AND the codec's per-group min / max from one read of ``input``
+    (the reference reads it once for each: ops.py:456-458 / :515 and qbnscheme.py:28-40).
+
+    Returns ``(mn, mx, mean, invstd)`` -- ``mn`` / ``mx`` shaped ``[N, G, 1]`` in the input's
+    dtype, ``mean`` / ``invstd`` float32 ``[C]`` -- or ``None`` when the geometry is not covered
+    (then the caller takes the two-read path).  ``running_mean`` / ``running_var`` are updated
+    when given; ``out``: optional float32 buffer of >= 2 * C elements for mean then invstd."""
+    if not input.is_cuda or not input.is_contiguous() or input.dim() < 2:
+        return None
+    N, C, HW = _bn_dims(input)
+    lib = _lib.load()
+    nbytes = lib.actnn_batch_norm_stats_minimax_workspace(N, C, HW)
+    if nbytes < 0:
+        return None
+    for t in (running_mean, running_var):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            return None
+    G = C * HW // 256
+    dev = input.device
+    mn = torch.empty((N, G, 1), dtype=input.dtype, device=dev)
+    mx = torch.empty((N, G, 1), dtype=input.dtype, device=dev)
+    if out is None:
+        out = torch.empty(2 * C, dtype=torch.float32, device=dev)
+    elif out.dtype != torch.float32 or not out.is_contiguous() or out.numel() < 2 * C or out.device != dev:
+        raise RuntimeError("batch_norm_stats_minimax: out must be a contiguous float32 tensor of >= 2*C elements")
+    w32, b32 = _as_f32(weight), _as_f32(bias)
+    ws = _lib.scratch(dev, nbytes)
+    _lib.call("actnn_batch_norm_stats_minimax", input, _lib.ptr(input), mn.data_ptr(), mx.data_ptr(), _lib.ptr(w32),
+              _lib.ptr(b32), _lib.ptr(running_mean), _lib.ptr(running_var), out.data_ptr(), out.data_ptr() + 4 * C,
+              N, C, HW, float(momentum), float(eps), _lib.dtype_id(input.dtype), ws.data_ptr(), nbytes,
+              _lib.stream_of(input))
+    flat = out.view(-1)
+    return mn, mx, flat[:C], flat[C:2 * C]
+
+
 def batch_norm_elemt(input, weight, bias, mean, invstd, eps):
     """``torch.batch_norm_elemt``: normalise with given statistics (ops.py:554)."""
     x = input.contiguous()
     N, C, HW = _bn_dims(x)
     y = torch.empty_like(x)
-    ws = torch.empty(max(16 * C, 16), dtype=torch.uint8, device=x.device)
+    ws = _lib.scratch(x.device, max(16 * C, 16))
     # the converted copies must outlive the call: a pointer taken from a temporary would dangle
     w32, b32, m32, i32 = _as_f32(weight), _as_f32(bias), _as_f32(mean), _as_f32(invstd)
     _lib.call("actnn_batch_norm_elemt", x, _lib.ptr(x), _lib.ptr(w32), _lib.ptr(b32), _lib.ptr(m32), _lib.ptr(i32),
@@ -195,7 +233,7 @@ def batch_norm_backward_elemt(grad_out, input, mean, invstd, weight, sum_dy, sum
     N, C, HW = _bn_dims(x)
     counts = count.reshape(-1).to(torch.float32).contiguous()
     dx = torch.empty_like(x)
-    ws = torch.empty(max(16 * C, 16), dtype=torch.uint8, device=x.device)
+    ws = _lib.scratch(x.device, max(16 * C, 16))
     w32, m32, i32 = _as_f32(weight), _as_f32(mean), _as_f32(invstd)       # kept alive across the call
     sdy, sdx = _as_f32(sum_dy), _as_f32(sum_dy_xmu)
     _lib.call("actnn_batch_norm_backward_elemt", x, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(w32),

@@ -95,12 +95,15 @@ def pack_mixed_precision(data, min, max, bits, stochastic, *, noise=None, philox
 
 
 def compress_mixed_precision(data, target_bits: int, initial_bits: int, range_factor: float, coeff: float = 1.0,
-                             grad_scale=None, stochastic=True, *, noise=None, philox=None, stat_dtype=None):
+                             grad_scale=None, stochastic=True, *, noise=None, philox=None, stat_dtype=None,
+                             minmax=None):
     """The adaptive compress of ``data [N, G, 256]`` in one native call: min/max,
     sensitivities, greedy allocation at ``target_bits`` total bits, pack.
 
     Equivalent to ``QScheme.compute_quantization_bits`` followed by ``pack_mixed_precision``
     (actnn/actnn/qscheme.py:57-94, ops.py:44-48) with no host synchronisation.
+    ``minmax=(mn, mx)``: the per-group extrema when a previous pass already produced them
+    (``backward_func.batch_norm_stats_minimax``); the activation is then read once, not twice.
     Returns ``(packed, bits, scale, min, C)``; ``packed.word_offsets`` is set."""
     check_cuda_tensor(data, "data", 3)
     n, g, gs = data.shape
@@ -115,12 +118,28 @@ def compress_mixed_precision(data, target_bits: int, initial_bits: int, range_fa
     bits = torch.empty(n, dtype=torch.int32, device=dev)
     offsets = torch.empty(n + 1, dtype=torch.int64, device=dev)
     C = torch.empty(n, dtype=torch.float32, device=dev)
-    ws_bytes = 2 * ((n * g * data.element_size() + 255) // 256 * 256) + 256     # actnn_compress_mixed_workspace
-    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     if grad_scale is not None and (grad_scale.dtype != torch.float32 or not grad_scale.is_cuda
                                    or grad_scale.numel() != 1):
         raise RuntimeError("grad_scale must be a float32 CUDA tensor with one element!")
     nz, seed, offset = _noise_args(data, stochastic, noise, philox)
+    if minmax is not None:
+        gmn, gmx = minmax
+        check_cuda_tensor(gmn, "min", dtype=data.dtype)
+        check_cuda_tensor(gmx, "max", dtype=data.dtype)
+        if gmn.numel() != n * g or gmx.numel() != n * g:
+            raise RuntimeError("min / max must have one element per group!")
+        workspace = _lib.scratch(dev, 256)
+        _lib.call("actnn_compress_mixed_prestat", data, data.data_ptr(), gmn.data_ptr(), gmx.data_ptr(),
+                  packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), bits.data_ptr(), offsets.data_ptr(),
+                  C.data_ptr(), workspace.data_ptr(), n, g, gs, _lib.dtype_id(data.dtype), _lib.dtype_id(sdt),
+                  float(range_factor), float(coeff), _lib.ptr(grad_scale), int(initial_bits), float(target_bits),
+                  int(bool(stochastic)), nz, seed, offset, _lib.stream_of(data))
+        packed.word_offsets = offsets
+        bits.word_offsets = offsets
+        bits.total_bits = total
+        return packed, bits, scale, mn, C
+    ws_bytes = 2 * ((n * g * data.element_size() + 255) // 256 * 256) + 256     # actnn_compress_mixed_workspace
+    workspace = _lib.scratch(dev, ws_bytes)
     _lib.call("actnn_compress_mixed", data, data.data_ptr(), packed.data_ptr(), scale.data_ptr(), mn.data_ptr(),
               bits.data_ptr(), offsets.data_ptr(), C.data_ptr(), workspace.data_ptr(), ws_bytes, n, g, gs,
               _lib.dtype_id(data.dtype), _lib.dtype_id(sdt), float(range_factor), float(coeff),

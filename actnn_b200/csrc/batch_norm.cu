@@ -306,6 +306,151 @@ __global__ void bn_backward_coef_kernel(const float* __restrict__ mean, const fl
   }
 }
 
+// ------------------------------------------------------------------ statistics + group min / max
+// The batch-norm statistics AND the per-group min / max of the activation codec from ONE read
+// of x (the reference reads x for the statistics, ops.py:456-458, and again for min / max,
+// qbnscheme.py:21-52).  The pass is organised like the codec: a sample is [G, 256] rows, a warp
+// task is R consecutive rows, lane t owns elements 8t..8t+7 of a row.  R * 256 <= HW, so a
+// task touches at most two channels and every lane adds its eight (x - shift) and their
+// squares to one of two slots; an octet never straddles channels because HW % 8 == 0.  A task
+// writes its four partial sums; the sums of a channel are added up by a second, tiny kernel in
+// a fixed order, so the statistics do not depend on scheduling.  `shift` is the channel's
+// first element, as in the plain reduce kernel above.
+struct StatMinimaxShape {
+  int N, C, HW, G, R, T;            // T = tasks per sample = ceil(G / R)
+  FastDiv hw;                       // element offset within a sample / HW = channel
+};
+
+template <typename T> ACTNN_DEV void oct_to_floats(const Oct<T>& o, float (&f)[8]);
+template <> ACTNN_DEV void oct_to_floats<float>(const Oct<float>& o, float (&f)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = o.f[j];
+}
+template <> ACTNN_DEV void oct_to_floats<__half>(const Oct<__half>& o, float (&f)[8]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&o.r[k]));
+    f[2 * k] = v.x; f[2 * k + 1] = v.y;
+  }
+}
+template <> ACTNN_DEV void oct_to_floats<__nv_bfloat16>(const Oct<__nv_bfloat16>& o, float (&f)[8]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    f[2 * k] = __uint_as_float(o.r[k] << 16);
+    f[2 * k + 1] = __uint_as_float(o.r[k] & 0xffff0000u);
+  }
+}
+
+constexpr int kStatRowsMax = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads)
+bn_stats_minimax_kernel(const T* __restrict__ x, StatMinimaxShape sh, T* __restrict__ mn, T* __restrict__ mx,
+                        float4* __restrict__ partial) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * kBnThreads + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * kBnThreads) >> 5;
+  const int64_t total = (int64_t)sh.N * sh.T;
+  for (int64_t task = warp; task < total; task += nwarps) {
+    const int n = (int)(task / sh.T), j = (int)(task - (int64_t)n * sh.T);
+    const int row0 = j * sh.R;
+    const int rows = min(sh.R, sh.G - row0);
+    const uint32_t e0 = (uint32_t)row0 * kGroup;                 // first element of the task within its sample
+    const uint32_t c0 = fdiv(e0, sh.hw);
+    const uint32_t boundary = (c0 + 1) * (uint32_t)sh.HW;        // first element of the next channel
+    const float shift0 = to_float<T>(__ldg(x + (int64_t)c0 * sh.HW));
+    const float shift1 = c0 + 1 < (uint32_t)sh.C ? to_float<T>(__ldg(x + (int64_t)(c0 + 1) * sh.HW)) : 0.f;
+    const T* base = x + ((int64_t)n * sh.G + row0) * kGroup + lane * kOct;
+    Oct<T> v[kStatRowsMax];
+#pragma unroll
+    for (int r = 0; r < kStatRowsMax; ++r) v[r] = r < rows ? load_oct<T>(base + r * kGroup) : zero_oct<T>();
+    float s0 = 0.f, q0 = 0.f, s1 = 0.f, q1 = 0.f, my_mn = 0.f, my_mx = 0.f;
+#pragma unroll
+    for (int r = 0; r < kStatRowsMax; ++r) {
+      if (r < rows) {                                              // warp-uniform
+        float lo, hi;
+        oct_minmax<T>(v[r], lo, hi);
+        lo = warp_min(lo);
+        hi = warp_max(hi);
+        if (lane == r) { my_mn = lo; my_mx = hi; }
+        const bool second = e0 + (uint32_t)(r * kGroup + lane * kOct) >= boundary;
+        const float shift = second ? shift1 : shift0;
+        float f[8], s = 0.f, q = 0.f;
+        oct_to_floats<T>(v[r], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float d = f[e] - shift;
+          s += d;
+          q = fmaf(d, d, q);
+        }
+        s0 += second ? 0.f : s; q0 += second ? 0.f : q;
+        s1 += second ? s : 0.f; q1 += second ? q : 0.f;
+      }
+    }
+    if (lane < rows) {
+      const int64_t g = (int64_t)n * sh.G + row0 + lane;
+      mn[g] = from_float<T>(my_mn);
+      mx[g] = from_float<T>(my_mx);
+    }
+    // four sums over the warp in 6 + 6 shuffle-adds: halves of the warp specialise on a slot,
+    // then quarters on sum / sum of squares; lanes 0, 8, 16, 24 end with s0, q0, s1, q1
+    {
+      const bool hi16 = lane & 16;
+      const float ks = hi16 ? s1 : s0, kq = hi16 ? q1 : q0;       // kept
+      const float gs = hi16 ? s0 : s1, gq = hi16 ? q0 : q1;       // given to the other half
+      float a = ks + __shfl_xor_sync(kFull, gs, 16);
+      float b = kq + __shfl_xor_sync(kFull, gq, 16);
+      const bool hi8 = lane & 8;
+      float t = (hi8 ? b : a) + __shfl_xor_sync(kFull, hi8 ? a : b, 8);
+      t += __shfl_xor_sync(kFull, t, 4);
+      t += __shfl_xor_sync(kFull, t, 2);
+      t += __shfl_xor_sync(kFull, t, 1);
+      if ((lane & 7) == 0) reinterpret_cast<float*>(partial + task)[lane >> 3] = t;
+    }
+  }
+}
+
+// One block per channel: adds the partial sums of every task that touches the channel (sample
+// after sample, task after task: a fixed order) and finishes like bn_forward_reduce_kernel.
+__global__ void __launch_bounds__(kBnThreads)
+bn_stats_finish_kernel(const float4* __restrict__ partial, StatMinimaxShape sh, const void* __restrict__ x, int dtype, const float* __restrict__ weight,
+                       const float* __restrict__ bias, float* __restrict__ running_mean,
+                       float* __restrict__ running_var, float* __restrict__ save_mean,
+                       float* __restrict__ save_invstd, float4* __restrict__ coef, float momentum, float eps) {
+  const int c = blockIdx.x;
+  const uint32_t span = (uint32_t)sh.R * kGroup;
+  const uint32_t first = (uint32_t)c * sh.HW, last = first + sh.HW - 1;
+  const int j_lo = (int)(first / span), j_hi = min((int)(last / span), sh.T - 1);
+  float sum = 0.f, sq = 0.f;
+  for (int n = threadIdx.x; n < sh.N; n += kBnThreads) {
+    for (int j = j_lo; j <= j_hi; ++j) {
+      const uint32_t c0 = fdiv((uint32_t)j * span, sh.hw);
+      const float4 p = __ldg(partial + (int64_t)n * sh.T + j);
+      if (c0 == (uint32_t)c) { sum += p.x; sq += p.y; }
+      else if (c0 + 1 == (uint32_t)c) { sum += p.z; sq += p.w; }
+    }
+  }
+  const float2 tot = block_sum2(sum, sq);
+  if (threadIdx.x != 0) return;
+  float shift;
+  if (dtype == ACTNN_F32) shift = reinterpret_cast<const float*>(x)[(int64_t)c * sh.HW];
+  else if (dtype == ACTNN_F16) shift = __half2float(reinterpret_cast<const __half*>(x)[(int64_t)c * sh.HW]);
+  else shift = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[(int64_t)c * sh.HW]);
+  const float M = (float)sh.N * (float)sh.HW;
+  const float m_s = tot.x / M;
+  const float var = fmaxf(tot.y / M - m_s * m_s, 0.f);
+  const float mean = shift + m_s;
+  const float invstd = 1.0f / sqrtf(var + eps);
+  save_mean[c] = mean;
+  save_invstd[c] = invstd;
+  if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mean;
+  if (running_var) {
+    const float unbiased = M > 1.f ? var * (M / (M - 1.f)) : var;
+    running_var[c] = (1.f - momentum) * running_var[c] + momentum * unbiased;
+  }
+  if (coef) coef[c] = make_float4(mean, invstd * (weight ? weight[c] : 1.f), bias ? bias[c] : 0.f, 0.f);
+}
+
 // ------------------------------------------------------------------ host side
 // Upper bound of the splits per channel (sizes the workspace): about 8 blocks per SM.
 int splits_for(int64_t N, int64_t C) {
@@ -470,6 +615,21 @@ int backward_apply_typed(const void* x, const void* dy, void* dx, const float4* 
   return check_launch();
 }
 
+// Geometry the fused statistics + min / max pass covers: groups must not need padding, an octet
+// must not straddle two channels and a row of 256 must not span more than two.
+bool stats_minimax_supported(int64_t N, int64_t C, int64_t HW) {
+  return N > 0 && C > 0 && HW >= kGroup && HW % 8 == 0 && (C * HW) % kGroup == 0 && check_shape(N, C, HW) == ACTNN_OK;
+}
+StatMinimaxShape stats_minimax_shape(int64_t N, int64_t C, int64_t HW) {
+  StatMinimaxShape sh;
+  sh.N = (int)N; sh.C = (int)C; sh.HW = (int)HW;
+  sh.G = (int)(C * HW / kGroup);
+  sh.R = (int)min((int64_t)kStatRowsMax, HW / kGroup);
+  sh.T = (sh.G + sh.R - 1) / sh.R;
+  sh.hw = make_fastdiv((uint32_t)HW);
+  return sh;
+}
+
 }  // namespace
 }  // namespace actnn
 
@@ -612,4 +772,44 @@ extern "C" int actnn_batch_norm_backward_elemt(const void* x, const void* grad_o
     case ACTNN_BF16: return backward_apply_typed<__nv_bfloat16>(x, grad_out, grad_in, coef, N, C, HW, s);
     default: return ACTNN_ERR_DTYPE;
   }
+}
+
+extern "C" int64_t actnn_batch_norm_stats_minimax_workspace(int64_t N, int64_t C, int64_t HW) {
+  if (!stats_minimax_supported(N, C, HW)) return -1;
+  const StatMinimaxShape sh = stats_minimax_shape(N, C, HW);
+  return ((int64_t)16 * N * sh.T + 16 * C + 255) / 256 * 256;
+}
+
+extern "C" int actnn_batch_norm_stats_minimax(const void* x, void* mn, void* mx, const float* weight,
+                                              const float* bias, float* running_mean, float* running_var,
+                                              float* save_mean, float* save_invstd, int64_t N, int64_t C, int64_t HW,
+                                              double momentum, double eps, int dtype, void* workspace,
+                                              int64_t workspace_bytes, actnn_stream_t stream) {
+  if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
+  if (!stats_minimax_supported(N, C, HW)) return ACTNN_ERR_SHAPE;
+  if (!x || !mn || !mx || !save_mean || !save_invstd || !workspace) return ACTNN_ERR_NULL;
+  if (workspace_bytes < actnn_batch_norm_stats_minimax_workspace(N, C, HW)) return ACTNN_ERR_CAPACITY;
+  if (!aligned(x, dtype == ACTNN_F32 ? 32 : 16) || !aligned(workspace, 16)) return ACTNN_ERR_ALIGN;
+  const StatMinimaxShape sh = stats_minimax_shape(N, C, HW);
+  float4* partial = (float4*)workspace;
+  float4* coef = partial + (int64_t)N * sh.T;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t tasks = (int64_t)N * sh.T;
+#define ACTNN_SM(T)                                                                                        \
+  {                                                                                                        \
+    auto kernel = bn_stats_minimax_kernel<T>;                                                              \
+    kernel<<<persistent_grid(kernel, kBnThreads, tasks), kBnThreads, 0, s>>>((const T*)x, sh, (T*)mn, (T*)mx, \
+                                                                             partial);                     \
+  }
+  switch (dtype) {
+    case ACTNN_F32: ACTNN_SM(float) break;
+    case ACTNN_F16: ACTNN_SM(__half) break;
+    default: ACTNN_SM(__nv_bfloat16) break;
+  }
+#undef ACTNN_SM
+  if (int st = check_launch()) return st;
+  bn_stats_finish_kernel<<<(unsigned)C, kBnThreads, 0, s>>>(partial, sh, x, dtype, weight, bias, running_mean,
+                                                           running_var, save_mean, save_invstd, coef,
+                                                           (float)momentum, (float)eps);
+  return check_launch();
 }

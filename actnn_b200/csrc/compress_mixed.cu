@@ -58,6 +58,42 @@ extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* sca
                          stat_dtype, stochastic, noise, seed, offset, true, (cudaStream_t)stream);
 }
 
+// The same compress when the per-group min / max already exist (actnn_batch_norm_stats_minimax
+// produces them in the pass that computes the batch-norm statistics): sensitivities + greedy
+// allocation, then the pack.  `ticket_workspace`: 256 bytes, 256-byte aligned.
+extern "C" int actnn_compress_mixed_prestat(const void* data, const void* mn, const void* mx, int32_t* packed,
+                                            void* scale, void* mn_out, int32_t* bits_out, int64_t* word_offsets_out,
+                                            float* C_out, void* ticket_workspace, int64_t N, int64_t G,
+                                            int64_t group_size, int dtype, int stat_dtype, float range_factor,
+                                            float coeff, const float* grad_scale, int initial_bits, double target,
+                                            int stochastic, const void* noise, uint64_t seed, uint64_t offset,
+                                            actnn_stream_t stream) {
+  if (N < 0 || G < 0 || group_size != kGroup) return ACTNN_ERR_SHAPE;
+  if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
+  if (initial_bits < 1 || initial_bits > 8) return ACTNN_ERR_BITS;
+  if (N == 0 || G == 0) return ACTNN_OK;
+  if (!data || !mn || !mx || !packed || !scale || !mn_out || !bits_out || !word_offsets_out || !C_out ||
+      !ticket_workspace)
+    return ACTNN_ERR_NULL;
+  if (!aligned(ticket_workspace, 256)) return ACTNN_ERR_ALIGN;
+  cudaStream_t s = (cudaStream_t)stream;
+  int st;
+  if (range_greedy_supported(N, initial_bits)) {
+    if (cudaMemsetAsync(ticket_workspace, 0, sizeof(unsigned), s) != cudaSuccess) return ACTNN_ERR_LAUNCH;
+    st = range_greedy_impl(mn, mx, N, G, dtype, range_factor, coeff, grad_scale, C_out, (unsigned*)ticket_workspace,
+                           initial_bits, target, bits_out, word_offsets_out, group_size, s);
+    if (st) return st;
+  } else {
+    st = actnn_range_sqr(mn, mx, N, G, dtype, range_factor, coeff, grad_scale, C_out, stream);
+    if (st) return st;
+    st = actnn_calc_precision(C_out, nullptr, N, initial_bits, target, bits_out, word_offsets_out, G, group_size,
+                              nullptr, 0, stream);
+    if (st) return st;
+  }
+  return pack_mixed_impl(data, mn, mx, bits_out, word_offsets_out, packed, scale, mn_out, N, G, group_size, dtype,
+                         stat_dtype, stochastic, noise, seed, offset, true, s);
+}
+
 // ------------------------------------------------------------------------------------------
 // The same compress for callers that have no way to provide scratch memory.
 //

@@ -92,8 +92,12 @@ def no_scheme_compute_quantization_bits(input):
     return groups, config.activation_compression_bits[0], mn, mx
 
 
-def quantize_activation(input, scheme):
-    """Compress one activation; returns ``(q_input, q_bits, q_scale, q_min)`` (ops.py:99-118)."""
+def quantize_activation(input, scheme, minmax=None):
+    """Compress one activation; returns ``(q_input, q_bits, q_scale, q_min)`` (ops.py:99-118).
+
+    ``minmax=(mn, mx)``: per-group extrema of ``input`` that a previous pass already produced
+    (the batch-norm Functions get them with their statistics); only schemes whose ``compress``
+    accepts them use them."""
     if not config.compress_activation:
         if config.swap:
             input = swap_to_cpu(input)
@@ -109,7 +113,10 @@ def quantize_activation(input, scheme):
         return q_input, q_bits, q_scale.to(stat_dtype), q_min.to(stat_dtype)
 
     if scheme:
-        fused = scheme.compress(input, stat_dtype) if hasattr(scheme, "compress") else None
+        if minmax is not None:
+            fused = scheme.compress(input, stat_dtype, minmax=minmax)
+        else:
+            fused = scheme.compress(input, stat_dtype) if hasattr(scheme, "compress") else None
         if fused is not None:
             q_input, q_bits, q_scale, q_min = fused
         else:
@@ -370,11 +377,34 @@ class linear(Function):
         return grad_input, grad_weight, grad_bias, None
 
 
+def _fused_bn_statistics(input, scheme, weight, bias, running_mean, running_var, momentum, eps, out=None):
+    """Statistics of a training-mode batch norm together with the group min / max its compressed
+    copy needs, from one read of ``input``; ``None`` when that pass does not apply (exact or
+    simulated activations, per-tensor ranges, a scheme without the one-call compress, or a
+    geometry the kernel does not cover)."""
+    if not (config.compress_activation and config.pergroup and not config.simulate and scheme is not None
+            and hasattr(scheme, "compress") and config.group_size == 256):
+        return None
+    return ext_backward_func.batch_norm_stats_minimax(input, weight, bias, running_mean, running_var, momentum, eps,
+                                                      out=out)
+
+
 class batch_norm(Function):
     @staticmethod
     def forward(ctx, input, running_mean, running_var, weight, bias, training, exponential_average_factor, eps,
                 scheme):
-        quantized = quantize_activation(input, scheme)
+        fused = None
+        if training and input.is_cuda:
+            input = input.contiguous()
+            fused = _fused_bn_statistics(input, scheme, weight, bias, running_mean, running_var,
+                                         exponential_average_factor, eps)
+        if fused is not None:
+            # one read of the input gave the statistics and the group ranges; the second read
+            # packs, the third normalises (the reference reads it four times)
+            mn, mx, save_mean, save_var = fused
+            quantized = quantize_activation(input, scheme, minmax=(mn, mx))
+        else:
+            quantized = quantize_activation(input, scheme)
         empty_cache(config.empty_cache_threshold)
         if config.debug_memory_op_forward:
             global bn_layer_ct, total_act_mem
@@ -384,7 +414,10 @@ class batch_norm(Function):
             total_act_mem += compute_tensor_bytes([t for t in quantized if isinstance(t, torch.Tensor)])
             print("Act mem: %.2f MB" % (total_act_mem / 1024 ** 2))
 
-        if training:
+        if fused is not None:
+            output = ext_backward_func.batch_norm_elemt(input, weight, bias, save_mean, save_var, eps)
+            reserve = torch.empty(0, dtype=torch.uint8, device=input.device)
+        elif training:
             output, save_mean, save_var, reserve = ext_backward_func.cudnn_batch_norm(
                 input, weight, bias, running_mean, running_var, training, exponential_average_factor, eps)
         else:
@@ -435,7 +468,10 @@ class sync_batch_norm(Function):
         local_count = input.numel() // num_channels
         # the gathered message [mean, invstd, count] is written in place: no cat / stack
         combined = torch.empty(2 * num_channels + 1, dtype=torch.float32, device=input.device)
-        ext_backward_func.batch_norm_stats(input, eps, out=combined)
+        # local statistics, with the group ranges of the compressed copy from the same read when possible
+        fused = _fused_bn_statistics(input, scheme, None, None, None, None, 0.0, eps, out=combined)
+        if fused is None:
+            ext_backward_func.batch_norm_stats(input, eps, out=combined)
         combined[2 * num_channels:].fill_(local_count)
         gathered = torch.empty(world_size, 2 * num_channels + 1, dtype=torch.float32, device=input.device)
         dist.all_gather_into_tensor(gathered, combined, process_group, async_op=False)
@@ -448,7 +484,7 @@ class sync_batch_norm(Function):
         mean, invstd = torch.batch_norm_gather_stats_with_counts(
             input, mean_all, invstd_all, running_mean, running_var, momentum, eps, count_all.reshape(-1))
 
-        self.saved = quantize_activation(input, scheme)
+        self.saved = quantize_activation(input, scheme, minmax=None if fused is None else fused[:2])
         self.save_for_backward(weight, mean, invstd, count_all)
         self.scheme = scheme
         self.other_args = (input.shape, input.dtype)

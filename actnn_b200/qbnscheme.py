@@ -29,8 +29,9 @@ class QBNScheme(QScheme):
         b.total_bits = total_bits_after_greedy(N, self.initial_bits, target)
         return groups, b, mn, mx
 
-    def compress(self, input, stat_dtype):
-        """One-call variant of ``compute_quantization_bits`` + pack (see ``QScheme.compress``)."""
+    def compress(self, input, stat_dtype, minmax=None):
+        """One-call variant of ``compute_quantization_bits`` + pack (see ``QScheme.compress``).
+        ``minmax``: group extrema already computed together with the batch-norm statistics."""
         if not config.pergroup:
             return None
         self.prev_linear = QScheme.prev_layer
@@ -38,7 +39,7 @@ class QBNScheme(QScheme):
         num_pixels = (input.numel() // N) // D
         q_input, b, q_scale, q_min, _ = ext_quantization.compress_mixed_precision(
             to_groups(input), int(self.bits * N), int(self.initial_bits), config.group_size / num_pixels,
-            1.0, None, config.stochastic, stat_dtype=stat_dtype)
+            1.0, None, config.stochastic, stat_dtype=stat_dtype, minmax=minmax)
         return q_input, b, q_scale, q_min
 
     @staticmethod

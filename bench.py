@@ -608,6 +608,7 @@ def resnet_throughput(level: str, batch: int, steps: int, warmup: int, dev, worl
     import actnn_b200 as actnn
     from actnn_b200.conf import QuantizationConfig
 
+    torch.cuda.reset_peak_memory_stats(dev)
     actnn.config.__dict__.update(QuantizationConfig().__dict__)
     actnn.QScheme.layers.clear()
     actnn.QBNScheme.layers.clear()

@@ -219,6 +219,41 @@ int actnn_compress_mixed_static(const void* data, int32_t* packed, void* scale, 
                                 uint64_t seed, uint64_t offset, actnn_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
+ * Batch-norm statistics and the codec's per-group min / max from ONE read of x.
+ * Replaces, for a quantized batch norm in training mode, the pair of reads the reference
+ * makes: the statistics inside at::cudnn_batch_norm (backward_func.cc:87, called at
+ * actnn/actnn/ops.py:456-458; torch.batch_norm_stats at ops.py:515 for the synchronised
+ * layer) and the min / max of QBNScheme.compute_quantization_bits (qbnscheme.py:28-40).
+ *   x           [N, C, HW] contiguous (NCHW), dtype float32 / float16 / bfloat16
+ *   mn, mx      [N * C * HW / 256] in x's dtype: min / max of every 256-element group of the
+ *               flattened samples (what actnn_minimax returns for the same tensor)
+ *   save_mean, save_invstd  float32 [C]; running_mean / running_var (may be NULL) are updated
+ *               with `momentum` exactly as actnn_batch_norm_forward does
+ *   weight, bias  only used to fill the coefficients kept in the workspace; may be NULL
+ * Geometry: HW % 8 == 0, HW >= 256 and C * HW % 256 == 0 (every layer of a ResNet down to
+ * 16x16 maps); anything else returns ACTNN_ERR_SHAPE and the caller takes the two-read path.
+ * actnn_batch_norm_stats_minimax_workspace returns the scratch bytes (-1: unsupported). */
+int64_t actnn_batch_norm_stats_minimax_workspace(int64_t N, int64_t C, int64_t HW);
+int actnn_batch_norm_stats_minimax(const void* x, void* mn, void* mx, const float* weight, const float* bias,
+                                   float* running_mean, float* running_var, float* save_mean, float* save_invstd,
+                                   int64_t N, int64_t C, int64_t HW, double momentum, double eps, int dtype,
+                                   void* workspace, int64_t workspace_bytes, actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * actnn_compress_mixed for an activation whose per-group min / max are already known (from
+ * actnn_batch_norm_stats_minimax or actnn_minimax): sensitivities, greedy allocation and pack,
+ * i.e. QBNScheme.compute_quantization_bits from its line qbnscheme.py:42 on, followed by
+ * pack_mixed_precision (quantization.cc:46-57).  `mn` / `mx` must be the true group extrema.
+ * `ticket_workspace`: 256 bytes of scratch, 256-byte aligned.  Other arguments as
+ * actnn_compress_mixed. */
+int actnn_compress_mixed_prestat(const void* data, const void* mn, const void* mx, int32_t* packed, void* scale,
+                                 void* mn_out, int32_t* bits_out, int64_t* word_offsets_out, float* C_out,
+                                 void* ticket_workspace, int64_t N, int64_t G, int64_t group_size, int dtype,
+                                 int stat_dtype, float range_factor, float coeff, const float* grad_scale,
+                                 int initial_bits, double target, int stochastic, const void* noise, uint64_t seed,
+                                 uint64_t offset, actnn_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
  * Mask ops.  The saved mask is 1 bit per element: bit (e % 8) of byte e / 8, padded to
  * whole int32 words (mask_words = ceil(numel / 32)).
  *

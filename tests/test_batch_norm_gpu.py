@@ -223,3 +223,83 @@ def test_resnet18_trains_like_stock_torch_at_level_L0(actnn, cuda_device):
         assert all(abs(a - b) <= 2e-2 * max(1.0, abs(a)) for a, b in zip(*losses)), losses
     finally:
         torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = tf32
+
+
+# ------------------------------------------------------------------------------ statistics + min / max in one read
+FUSED_SHAPES = [
+    (8, 64, 56, 56),      # HW = 3136: tasks of 8 rows, two channels per task at most
+    (4, 256, 28, 28),     # HW = 784: tasks of 3 rows, most groups straddle two channels
+    (3, 16, 16, 16),      # HW = 256: one row per task, a group is exactly a channel plane
+    (2, 6, 32, 40),       # HW = 1280, ragged last task of every sample
+    (5, 64, 112, 112),    # the stem of a ResNet
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", FUSED_SHAPES)
+def test_statistics_and_group_minmax_from_one_read(cuda_device, shape, dtype):
+    """``batch_norm_stats_minimax``: min / max of every 256-group exactly as the minimax kernel
+    (and ``torch.min/max``) gives them, statistics and running statistics as the plain batch-norm
+    kernels / ``torch.batch_norm_stats`` give them."""
+    from actnn_b200.cpp_extension import backward_func as bf
+    x, _, w, b, rm, rv = _inputs(shape, dtype, cuda_device, seed=3)
+    rm_ref, rv_ref = rm.clone(), rv.clone()
+    got = bf.batch_norm_stats_minimax(x, w, b, rm, rv, 0.1, 1e-5)
+    assert got is not None
+    mn, mx, mean, invstd = got
+    groups = x.reshape(shape[0], -1, 256)
+    assert torch.equal(mn.view(shape[0], -1), groups.min(dim=2)[0])
+    assert torch.equal(mx.view(shape[0], -1), groups.max(dim=2)[0])
+    mean_t, invstd_t = torch.batch_norm_stats(x.float(), 1e-5)
+    assert _close(mean, mean_t, 2e-5) and _close(invstd, invstd_t, 2e-4)
+    # running statistics: the same update the unfused kernel makes
+    _, save_mean, save_invstd, _ = bf.cudnn_batch_norm(x, w, b, rm_ref, rv_ref, True, 0.1, 1e-5)
+    assert _close(mean, save_mean, 1e-5) and _close(invstd, save_invstd, 1e-4)
+    assert _close(rm, rm_ref, 1e-5) and _close(rv, rv_ref, 1e-4)
+    # bit-reproducible
+    mn2, mx2, mean2, invstd2 = bf.batch_norm_stats_minimax(x, w, b, None, None, 0.1, 1e-5)
+    assert torch.equal(mean2, mean) and torch.equal(invstd2, invstd) and torch.equal(mn2, mn)
+
+
+def test_statistics_and_minmax_pass_declines_other_geometries(cuda_device):
+    from actnn_b200.cpp_extension import backward_func as bf
+    for shape in ((16, 32, 14, 14), (16, 48, 7, 7), (4, 3, 16, 24), (64, 10)):
+        x = torch.randn(shape, device=cuda_device)
+        assert bf.batch_norm_stats_minimax(x, None, None, None, None, 0.1, 1e-5) is None
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_quantized_batch_norm_takes_the_one_read_path_and_matches_the_two_read_path(actnn, cuda_device, dtype):
+    """ops.batch_norm at level L3 on a covered geometry: output, gradients and the saved
+    compressed activation are the same as with the separate minimax and statistics passes."""
+    from actnn_b200 import ops
+    from actnn_b200.cpp_extension import backward_func as bf
+    actnn.set_optimization_level("L3")
+    N, C, H, W = 6, 32, 16, 24
+    x, gy, w, b, rm, rv = _inputs((N, C, H, W), dtype, cuda_device, seed=5)
+    gen = torch.cuda.default_generators[cuda_device.index or 0]
+    results = []
+    for fused in (True, False):
+        scheme = actnn.QBNScheme()
+        real = bf.batch_norm_stats_minimax
+        calls = []
+        if fused:
+            bf.batch_norm_stats_minimax = lambda *a, **k: (calls.append(1), real(*a, **k))[1]
+        else:
+            bf.batch_norm_stats_minimax = lambda *a, **k: None
+        try:
+            gen.manual_seed(77)
+            xi = x.clone().requires_grad_(True)
+            wi, bi = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+            rmi, rvi = rm.clone(), rv.clone()
+            y = ops.batch_norm.apply(xi, rmi, rvi, wi, bi, True, 0.1, 1e-5, scheme)
+            y.backward(gy)
+        finally:
+            bf.batch_norm_stats_minimax = real
+        assert bool(calls) == fused
+        results.append((y.detach(), xi.grad, wi.grad, bi.grad, rmi, rvi))
+    tol = TOL[dtype]
+    for a, r in zip(*results):
+        assert _close(a, r, 4 * tol)
+    ref = torch.nn.functional.batch_norm(x.float(), rm.clone(), rv.clone(), w, b, True, 0.1, 1e-5)
+    assert _close(results[0][0].float(), ref, 4 * tol)

@@ -31,7 +31,7 @@ def test_header_and_binding_agree(lib):
         assert hasattr(lib, name), "libactnn_b200.so does not export " + name
     bound = set(_lib.SIGNATURES) | {"actnn_status_string", "actnn_abi_version", "actnn_compress_mixed_workspace",
                                      "actnn_compress_mixed_static_capacity", "actnn_calc_precision_workspace",
-                                     "actnn_batch_norm_workspace"}
+                                     "actnn_batch_norm_workspace", "actnn_batch_norm_stats_minimax_workspace"}
     assert bound == set(names)
 
 

@@ -158,3 +158,38 @@ def test_max_pool_entry_points_stay_inside_their_outputs(env, geom, dtype):
     dx = Guarded(n * c * h * w, dtype, dev)
     _check(_lib, lib.actnn_max_pool2d_backward(y.ptr(), idx.ptr(), dx.ptr(), n, c, h, w, k, k, s, s, p, p, 1, 1, D, st),
            "actnn_max_pool2d_backward", {"dx": dx})
+
+
+@pytest.mark.parametrize("dtype", DTS)
+@pytest.mark.parametrize("shape", [(1, 1, 256), (3, 8, 288), (2, 5, 1280)])
+def test_statistics_minmax_pass_stays_inside_its_outputs(env, shape, dtype):
+    """actnn_batch_norm_stats_minimax and actnn_compress_mixed_prestat with guarded buffers."""
+    lib, _lib, q, dev = env
+    n, c, hw = shape
+    if (c * hw) % 256:
+        pytest.skip("geometry needs padding")
+    D = _lib.dtype_id(dtype)
+    sdt = torch.bfloat16 if dtype == torch.float32 else dtype
+    S = _lib.dtype_id(sdt)
+    st = torch.cuda.current_stream().cuda_stream
+    g = c * hw // 256
+    x = torch.randn(n, c, hw, generator=torch.Generator().manual_seed(hw)).to(dtype).to(dev)
+    nbytes = lib.actnn_batch_norm_stats_minimax_workspace(n, c, hw)
+    assert nbytes > 0
+    bufs = {"min": Guarded(n * g, dtype, dev), "max": Guarded(n * g, dtype, dev), "mean": Guarded(c, torch.float32, dev),
+            "invstd": Guarded(c, torch.float32, dev), "workspace": Guarded(nbytes, torch.uint8, dev)}
+    _check(_lib, lib.actnn_batch_norm_stats_minimax(x.data_ptr(), bufs["min"].ptr(), bufs["max"].ptr(), None, None,
+                                                    None, None, bufs["mean"].ptr(), bufs["invstd"].ptr(), n, c, hw,
+                                                    0.1, 1e-5, D, bufs["workspace"].ptr(), nbytes, st),
+           "actnn_batch_norm_stats_minimax", bufs)
+    total = 2 * n
+    cm = {"packed": Guarded(total * g * 256 // 32, torch.int32, dev), "scale": Guarded(n * g, sdt, dev),
+          "min_out": Guarded(n * g, sdt, dev), "bits": Guarded(n, torch.int32, dev),
+          "word_offsets": Guarded(n + 1, torch.int64, dev), "C": Guarded(n, torch.float32, dev),
+          "ticket": Guarded(256, torch.uint8, dev)}
+    _check(_lib, lib.actnn_compress_mixed_prestat(x.data_ptr(), bufs["min"].ptr(), bufs["max"].ptr(),
+                                                  cm["packed"].ptr(), cm["scale"].ptr(), cm["min_out"].ptr(),
+                                                  cm["bits"].ptr(), cm["word_offsets"].ptr(), cm["C"].ptr(),
+                                                  cm["ticket"].ptr(), n, g, 256, D, S, 1.0, 1.0, None, 8, float(total),
+                                                  1, None, 5, 0, st), "actnn_compress_mixed_prestat", cm)
+    assert int(cm["bits"].t.sum()) == total
