@@ -85,8 +85,13 @@ def test_sync_batch_norm_two_ranks_unequal_batches(tmp_path):
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     port = 29600 + os.getpid() % 300
+    import time
     ctx = mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=False)
-    if not ctx.join(timeout=180):
+    deadline = time.time() + 180
+    done = False
+    while not done and time.time() < deadline:           # join() returns as soon as ONE child has ended
+        done = ctx.join(timeout=5)
+    if not done:
         for proc in ctx.processes:                      # exactly the children started above
             if proc.is_alive():
                 proc.kill()
