@@ -22,7 +22,15 @@ import torch
 from .. import _lib
 from ._checks import check_cuda_tensor
 
-GROUP_SIZE = 256
+GROUP_SIZE = 256            # the size the fast kernels are written for; other multiples of 32 take a generic path
+MAX_GROUP_SIZE = 8192
+
+
+def _check_group_size(gs: int) -> None:
+    if gs % 32 != 0 or gs <= 32:
+        raise RuntimeError("Expected group_size % 32 == 0 (and group_size > 32) to be true, but got false.")
+    if gs > MAX_GROUP_SIZE:
+        raise RuntimeError("actnn_b200: group sizes above %d are not supported" % MAX_GROUP_SIZE)
 
 
 def _noise_args(data: torch.Tensor, stochastic: bool, noise: Optional[torch.Tensor], philox):
@@ -65,8 +73,7 @@ def pack_mixed_precision(data, min, max, bits, stochastic, *, noise=None, philox
     n, g, gs = data.shape
     if gs % 32 != 0:
         raise RuntimeError("Expected group_size % bits_per_int == 0 to be true, but got false.")
-    if gs != GROUP_SIZE:
-        raise RuntimeError("actnn_b200: only group_size 256 is supported")
+    _check_group_size(gs)
     if word_offsets is None:
         word_offsets = bits_prefix(bits, g, gs)
     if total_bits is None:
@@ -107,8 +114,7 @@ def compress_mixed_precision(data, target_bits: int, initial_bits: int, range_fa
     Returns ``(packed, bits, scale, min, C)``; ``packed.word_offsets`` is set."""
     check_cuda_tensor(data, "data", 3)
     n, g, gs = data.shape
-    if gs != GROUP_SIZE:
-        raise RuntimeError("actnn_b200: only group_size 256 is supported")
+    _check_group_size(gs)
     sdt = _stat_dtype(data.dtype, stat_dtype)
     total = min(initial_bits * n, max(int(target_bits), n))        # what the greedy ends with
     dev = data.device
@@ -159,8 +165,7 @@ def unpack_mixed_precision(data, bits, scale, min, N, num_groups, group_size, *,
     check_cuda_tensor(min, "min", 3, scale.dtype)
     if group_size % 32 != 0:
         raise RuntimeError("Expected group_size % 32 == 0 to be true, but got false.")
-    if group_size != GROUP_SIZE:
-        raise RuntimeError("actnn_b200: only group_size 256 is supported")
+    _check_group_size(group_size)
     out_dtype = scale.dtype if out_dtype is None else out_dtype
     _stat_dtype(out_dtype, scale.dtype)
     if word_offsets is None:
@@ -193,8 +198,7 @@ def pack_single_precision(data, min, max, bits, stochastic, *, noise=None, philo
     check_cuda_tensor(max, "max", 3, data.dtype)
     _check_single_bits(bits)
     n, g, gs = data.shape
-    if gs != GROUP_SIZE:
-        raise RuntimeError("actnn_b200: only group_size 256 is supported")
+    _check_group_size(gs)
     sdt = _stat_dtype(data.dtype, stat_dtype)
     packed = torch.empty(single_precision_bytes(bits, n, g, gs), dtype=torch.int8, device=data.device)
     scale = torch.empty((n, g, 1), dtype=sdt, device=data.device)
@@ -217,8 +221,7 @@ def compress_single_precision(data, bits, stochastic=True, *, noise=None, philox
     check_cuda_tensor(data, "data", 3)
     _check_single_bits(bits)
     n, g, gs = data.shape
-    if gs != GROUP_SIZE:
-        raise RuntimeError("actnn_b200: only group_size 256 is supported")
+    _check_group_size(gs)
     sdt = _stat_dtype(data.dtype, stat_dtype)
     packed = torch.empty(single_precision_bytes(bits, n, g, gs), dtype=torch.int8, device=data.device)
     scale = torch.empty((n, g, 1), dtype=sdt, device=data.device)
@@ -238,8 +241,7 @@ def unpack_single_precision(data, bits, scale, min, N, num_groups, group_size, *
     check_cuda_tensor(scale, "scale", 3)
     check_cuda_tensor(min, "min", 3, scale.dtype)
     _check_single_bits(bits)
-    if group_size != GROUP_SIZE:
-        raise RuntimeError("actnn_b200: only group_size 256 is supported")
+    _check_group_size(group_size)
     out_dtype = scale.dtype if out_dtype is None else out_dtype
     _stat_dtype(out_dtype, scale.dtype)
     out = torch.empty((N, num_groups, group_size), dtype=out_dtype, device=data.device)

@@ -13,7 +13,7 @@ import sys
 from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["api.cu", "codec_mixed.cu", "codec_single.cu", "compress_mixed.cu", "stats.cu", "mask_ops.cu",
+SOURCES = ["api.cu", "codec_mixed.cu", "codec_single.cu", "codec_generic.cu", "compress_mixed.cu", "stats.cu", "mask_ops.cu",
            "maxpool.cu", "batch_norm.cu"]
 HEADERS = ["common.cuh", "quant_math.cuh", os.path.join("..", "..", "include", "actnn_b200.h")]
 LIB = os.path.join(HERE, "libactnn_b200.so")

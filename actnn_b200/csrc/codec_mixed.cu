@@ -828,7 +828,7 @@ int launch_unpack(const int32_t* packed, const int32_t* bits, const int64_t* wor
 
 int check_common(int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype) {
   if (N < 0 || G < 0) return ACTNN_ERR_SHAPE;
-  if (group_size != kGroup) return ACTNN_ERR_SHAPE;
+  if (group_size != kGroup && !generic_group_ok(group_size)) return ACTNN_ERR_SHAPE;
   if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
   if (!(stat_dtype == dtype || (dtype == ACTNN_F32 && stat_dtype == ACTNN_BF16))) return ACTNN_ERR_DTYPE;
   if (N > (int64_t)1 << 40 || G > (int64_t)1 << 40 || (G && N > ((int64_t)1 << 52) / G)) return ACTNN_ERR_SHAPE;
@@ -858,6 +858,9 @@ int pack_mixed_impl(const void* data, const void* mn, const void* mx, const int3
   if (int st = check_common(N, G, group_size, dtype, stat_dtype)) return st;
   if (N == 0 || G == 0) return ACTNN_OK;
   if (!data || !mn || !mx || !bits || !word_offsets || !packed || !scale) return ACTNN_ERR_NULL;
+  if (group_size != kGroup)
+    return pack_mixed_generic(data, mn, mx, bits, word_offsets, packed, scale, mn_out, N, G, group_size, dtype,
+                              stat_dtype, stochastic, noise, seed, offset, s);
   const size_t al = dtype == ACTNN_F32 ? 32 : 16;
   if (!aligned(data, al) || (noise && !aligned(noise, al)) || !aligned(packed, 4)) return ACTNN_ERR_ALIGN;
   switch (dtype) {
@@ -898,8 +901,10 @@ extern "C" int actnn_unpack_mixed(const int32_t* packed, const int32_t* bits, co
   if (int st = check_common(N, G, group_size, dtype, stat_dtype)) return st;
   if (N == 0 || G == 0) return ACTNN_OK;
   if (!packed || !bits || !word_offsets || !scale || !mn || !out) return ACTNN_ERR_NULL;
-  if (!aligned(out, dtype == ACTNN_F32 ? 32 : 16) || !aligned(packed, 4)) return ACTNN_ERR_ALIGN;
   cudaStream_t s = (cudaStream_t)stream;
+  if (group_size != kGroup)
+    return unpack_mixed_generic(packed, bits, word_offsets, scale, mn, out, N, G, group_size, dtype, stat_dtype, s);
+  if (!aligned(out, dtype == ACTNN_F32 ? 32 : 16) || !aligned(packed, 4)) return ACTNN_ERR_ALIGN;
   switch (dtype) {
     case ACTNN_F16: return launch_unpack<__half, __half>(packed, bits, word_offsets, scale, mn, out, N, G, s);
     case ACTNN_BF16:

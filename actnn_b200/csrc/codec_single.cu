@@ -430,7 +430,7 @@ int launch_unpack(int bits, const int8_t* packed, const void* scale, const void*
 
 int check_common(int bits, int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype) {
   if (!(bits == 1 || bits == 2 || bits == 4 || bits == 8)) return ACTNN_ERR_BITS;
-  if (N < 0 || G < 0 || group_size != kGroup) return ACTNN_ERR_SHAPE;
+  if (N < 0 || G < 0 || (group_size != kGroup && !generic_group_ok(group_size))) return ACTNN_ERR_SHAPE;
   if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
   if (!(stat_dtype == dtype || (dtype == ACTNN_F32 && stat_dtype == ACTNN_BF16))) return ACTNN_ERR_DTYPE;
   if (N > (int64_t)1 << 40 || G > (int64_t)1 << 40 || (G && N > ((int64_t)1 << 52) / G)) return ACTNN_ERR_SHAPE;
@@ -448,6 +448,9 @@ int pack_entry(const void* data, const void* mn, const void* mx, int bits, int8_
     return cudaMemsetAsync(packed, 0, 1, s) == cudaSuccess ? ACTNN_OK : ACTNN_ERR_LAUNCH;
   }
   if (!data || !scale || (!FUSED && (!mn || !mx)) || (FUSED && !mn_out)) return ACTNN_ERR_NULL;
+  if (group_size != kGroup)
+    return pack_single_generic(FUSED, data, mn, mx, bits, packed, scale, mn_out, mx_out, N, G, group_size, dtype,
+                               stat_dtype, stochastic, noise, seed, offset, s);
   const size_t al = dtype == ACTNN_F32 ? 32 : 16;
   if (!aligned(data, al) || (noise && !aligned(noise, al)) || !aligned(packed, 8)) return ACTNN_ERR_ALIGN;
   switch (dtype) {
@@ -493,8 +496,10 @@ extern "C" int actnn_unpack_single(const int8_t* packed, int bits, const void* s
   if (int st = check_common(bits, N, G, group_size, dtype, stat_dtype)) return st;
   if (N == 0 || G == 0) return ACTNN_OK;
   if (!packed || !scale || !mn || !out) return ACTNN_ERR_NULL;
-  if (!aligned(out, dtype == ACTNN_F32 ? 32 : 16) || !aligned(packed, 8)) return ACTNN_ERR_ALIGN;
   cudaStream_t s = (cudaStream_t)stream;
+  if (group_size != kGroup)
+    return unpack_single_generic(packed, bits, scale, mn, out, N, G, group_size, dtype, stat_dtype, s);
+  if (!aligned(out, dtype == ACTNN_F32 ? 32 : 16) || !aligned(packed, 8)) return ACTNN_ERR_ALIGN;
   switch (dtype) {
     case ACTNN_F16: return launch_unpack<__half, __half>(bits, packed, scale, mn, out, N, G, s);
     case ACTNN_BF16: return launch_unpack<__nv_bfloat16, __nv_bfloat16>(bits, packed, scale, mn, out, N, G, s);

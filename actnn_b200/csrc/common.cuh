@@ -270,6 +270,22 @@ int range_greedy_impl(const void* mn, const void* mx, int64_t N, int64_t G, int 
                       float coeff, const float* grad_scale, float* C, unsigned* ticket, int initial_bits,
                       double target, int32_t* b_out, int64_t* word_offsets, int64_t group_size, cudaStream_t stream);
 
+// codec_generic.cu: the codec for group sizes other than 256 (multiples of 32), one warp per group.
+bool generic_group_ok(int64_t group_size);
+int pack_mixed_generic(const void* data, const void* mn, const void* mx, const int32_t* bits,
+                       const int64_t* word_offsets, int32_t* packed, void* scale, void* mn_out, int64_t N, int64_t G,
+                       int64_t gs, int dtype, int stat_dtype, int stochastic, const void* noise, uint64_t seed,
+                       uint64_t offset, cudaStream_t s);
+int unpack_mixed_generic(const int32_t* packed, const int32_t* bits, const int64_t* word_offsets, const void* scale,
+                         const void* mn, void* out, int64_t N, int64_t G, int64_t gs, int dtype, int stat_dtype,
+                         cudaStream_t s);
+int pack_single_generic(bool fused, const void* data, const void* mn, const void* mx, int bits, int8_t* packed,
+                        void* scale, void* mn_out, void* mx_out, int64_t N, int64_t G, int64_t gs, int dtype,
+                        int stat_dtype, int stochastic, const void* noise, uint64_t seed, uint64_t offset,
+                        cudaStream_t s);
+int unpack_single_generic(const int8_t* packed, int bits, const void* scale, const void* mn, void* out, int64_t N,
+                          int64_t G, int64_t gs, int dtype, int stat_dtype, cudaStream_t s);
+
 static inline bool aligned(const void* p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 
 #ifdef __CUDACC__

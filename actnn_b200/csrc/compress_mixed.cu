@@ -24,7 +24,7 @@ extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* sca
                                     int stat_dtype, float range_factor, float coeff, const float* grad_scale,
                                     int initial_bits, double target, int stochastic, const void* noise,
                                     uint64_t seed, uint64_t offset, actnn_stream_t stream) {
-  if (N < 0 || G < 0 || group_size != kGroup) return ACTNN_ERR_SHAPE;
+  if (N < 0 || G < 0 || (group_size != kGroup && !generic_group_ok(group_size))) return ACTNN_ERR_SHAPE;
   if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
   if (initial_bits < 1 || initial_bits > 8) return ACTNN_ERR_BITS;
   if (N == 0 || G == 0) return ACTNN_OK;
@@ -68,7 +68,7 @@ extern "C" int actnn_compress_mixed_prestat(const void* data, const void* mn, co
                                             float coeff, const float* grad_scale, int initial_bits, double target,
                                             int stochastic, const void* noise, uint64_t seed, uint64_t offset,
                                             actnn_stream_t stream) {
-  if (N < 0 || G < 0 || group_size != kGroup) return ACTNN_ERR_SHAPE;
+  if (N < 0 || G < 0 || (group_size != kGroup && !generic_group_ok(group_size))) return ACTNN_ERR_SHAPE;
   if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
   if (initial_bits < 1 || initial_bits > 8) return ACTNN_ERR_BITS;
   if (N == 0 || G == 0) return ACTNN_OK;
