@@ -63,7 +63,7 @@ def test_host_side_validation_needs_no_gpu(lib):
     assert lib.actnn_minimax(8, 16, 16, 4, 256, 1, None) == ALIGN
     # pack / unpack
     assert lib.actnn_pack_single(None, None, None, 3, None, None, None, 1, 1, 256, 0, 0, 1, None, 0, 0, None) == BITS
-    assert lib.actnn_pack_single(None, None, None, 2, None, None, None, 1, 1, 128, 0, 0, 1, None, 0, 0, None) == SHAPE
+    assert lib.actnn_pack_single(None, None, None, 2, None, None, None, 1, 1, 100, 0, 0, 1, None, 0, 0, None) == SHAPE   # not a multiple of 32
     assert lib.actnn_pack_single(None, None, None, 2, None, None, None, 1, 1, 256, 1, 0, 1, None, 0, 0, None) == DTYPE
     assert lib.actnn_pack_single(None, None, None, 2, None, None, None, 1, 1, 256, 0, 0, 1, None, 0, 0, None) == NULL
     assert lib.actnn_pack_mixed(None, None, None, None, None, None, None, None, -1, 1, 256, 0, 0, 1, None, 0, 0, None) == SHAPE
@@ -91,7 +91,7 @@ def test_host_side_validation_needs_no_gpu(lib):
     args = [256] * 8 + [8, 4, 3, 256, 1, 1, 1.0, 1.0, None, 8, 8.0, 1, None, 0, 0, None]
     assert lib.actnn_compress_mixed(*args) == 8                      # ACTNN_ERR_CAPACITY: workspace too small
     args[8] = 1 << 20
-    args[11] = 128
+    args[11] = 100                                                   # group size not a multiple of 32
     assert lib.actnn_compress_mixed(*args) == SHAPE
 
 
