@@ -100,27 +100,32 @@ int launch_minimax(const void* data, void* mn, void* mx, int64_t rows, int64_t c
 
 // ---------------------------------------------------------------------------- range_sqr
 // One block per sample; fixed-shape tree reduction, hence deterministic.
-// The first kThreads threads of the block do the work (a wider block gives the same sums).
-template <typename ST>
-ACTNN_DEV void range_sqr_block(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t n, int64_t G,
-                               float range_factor, float coeff, const float* __restrict__ grad_scale,
+// Every kThreads threads of the block take one sample (a block of THREADS threads takes
+// THREADS / kThreads consecutive samples); the order of the additions of a sample does not
+// depend on the block width, so every caller gets the same sums.
+template <typename ST, int THREADS>
+ACTNN_DEV void range_sqr_block(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t first_sample, int64_t N,
+                               int64_t G, float range_factor, float coeff, const float* __restrict__ grad_scale,
                                float* __restrict__ C) {
-  __shared__ float partial[kThreads / 32];
-  if (threadIdx.x < kThreads) {
+  constexpr int SUBS = THREADS / kThreads;
+  __shared__ float partial[SUBS][kThreads / 32];
+  const int sub = threadIdx.x / kThreads, t = threadIdx.x % kThreads;
+  const int64_t n = first_sample + sub;
+  if (n < N) {
     float acc = 0.f;
-    for (int64_t g = threadIdx.x; g < G; g += kThreads) {
+    for (int64_t g = t; g < G; g += kThreads) {
       const float d = round_to<ST>(__fsub_rn(load_scalar<ST>(mx, n * G + g), load_scalar<ST>(mn, n * G + g)));
       acc = __fmaf_rn(d, d, acc);
     }
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(kFull, acc, s);
-    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
+    if ((t & 31) == 0) partial[sub][t >> 5] = acc;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (t == 0 && n < N) {
     float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < kThreads / 32; ++i) tot += partial[i];
+    for (int i = 0; i < kThreads / 32; ++i) tot += partial[sub][i];
     const float r = round_to<ST>(sqrtf(tot));                  // torch.norm returns the stats' dtype
     float c = __fmul_rn(__fmul_rn(r, r), range_factor);        // .float().square() * (gs / num_pixels)
     c = __fmul_rn(coeff, c);
@@ -133,7 +138,7 @@ template <typename ST>
 __global__ void __launch_bounds__(kThreads)
 range_sqr_kernel(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_t G, float range_factor,
                  float coeff, const float* __restrict__ grad_scale, float* __restrict__ C) {
-  range_sqr_block<ST>(mn, mx, blockIdx.x, G, range_factor, coeff, grad_scale, C);
+  range_sqr_block<ST, kThreads>(mn, mx, blockIdx.x, gridDim.x, G, range_factor, coeff, grad_scale, C);
 }
 
 // ---------------------------------------------------------------------------- sample_sumsq
@@ -526,7 +531,8 @@ greedy_sample_kernel(const float* __restrict__ C, int N, int initial_bits, doubl
   greedy_block<THREADS>(c, N, initial_bits, target, coef, b_out, word_offsets, words_per_bit);
 }
 
-// Sensitivities and bit allocation of one layer in ONE launch: block n computes C[n]; the
+// Sensitivities and bit allocation of one layer in ONE launch: a block computes C[n] of
+// THREADS / 256 consecutive samples (so that all blocks are resident at once); the
 // block that takes the last ticket (no block waits for another) then runs the greedy over all
 // N sensitivities and leaves the ticket at zero for the next call on the same workspace.
 template <typename ST, int THREADS>
@@ -535,11 +541,13 @@ range_greedy_kernel(const ST* __restrict__ mn, const ST* __restrict__ mx, int64_
                     float coeff, const float* __restrict__ grad_scale, float* __restrict__ C, unsigned* ticket,
                     int N, int initial_bits, double target, GreedyCoef coef, int32_t* __restrict__ b_out,
                     int64_t* __restrict__ word_offsets, int64_t words_per_bit) {
-  static_assert(THREADS >= kThreads, "the range reduction uses kThreads threads");
+  static_assert(THREADS % kThreads == 0, "whole samples per block");
   __shared__ bool last;
-  range_sqr_block<ST>(mn, mx, blockIdx.x, G, range_factor, coeff, grad_scale, C);
+  range_sqr_block<ST, THREADS>(mn, mx, (int64_t)blockIdx.x * (THREADS / kThreads), N, G, range_factor, coeff,
+                               grad_scale, C);
+  __syncthreads();                                             // every C[n] of this block is written
   if (threadIdx.x == 0) {
-    __threadfence();                                           // C[n] before the ticket
+    __threadfence();                                           // ... and visible before the ticket
     last = atomicAdd(ticket, 1u) == gridDim.x - 1;
   }
   __syncthreads();
@@ -694,7 +702,7 @@ int range_greedy_impl(const void* mn, const void* mx, int64_t N, int64_t G, int 
   const int64_t wpb = G * group_size / 32;
   const int n = (int)N;
 #define ACTNN_RG(ST, T)                                                                                     \
-  range_greedy_kernel<ST, T><<<n, T, 0, s>>>((const ST*)mn, (const ST*)mx, G, range_factor, coeff, grad_scale, C, \
+  range_greedy_kernel<ST, T><<<(n + T / 256 - 1) / (T / 256), T, 0, s>>>((const ST*)mn, (const ST*)mx, G, range_factor, coeff, grad_scale, C, \
                                              ticket, n, initial_bits, target, coef, b_out, word_offsets, wpb)
 #define ACTNN_RG_N(ST)                                     \
   if (n <= 256) ACTNN_RG(ST, 256);                         \
