@@ -849,6 +849,11 @@ def run_profile(args):
     calls["batch_norm_backward"] = lambda: lib.actnn_batch_norm_backward(
         x.data_ptr(), dy.data_ptr(), w.data_ptr(), sm.data_ptr(), si.data_ptr(), out.data_ptr(), gw.data_ptr(),
         gb.data_ptr(), N, bn_c, bn_hw, F16, ws.data_ptr(), ws_bytes, st)
+    sm_bytes = lib.actnn_batch_norm_stats_minimax_workspace(N, bn_c, bn_hw)
+    sm_ws = torch.empty(max(sm_bytes, 16), dtype=torch.uint8, device=dev)
+    calls["batch_norm_stats_minimax"] = lambda: lib.actnn_batch_norm_stats_minimax(
+        x.data_ptr(), mn.data_ptr(), mx.data_ptr(), w.data_ptr(), bvec.data_ptr(), rm.data_ptr(), rv.data_ptr(),
+        sm.data_ptr(), si.data_ptr(), N, bn_c, bn_hw, 0.1, 1e-5, F16, sm_ws.data_ptr(), sm_bytes, st)
     calls["batch_norm_forward"]()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
