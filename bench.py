@@ -765,6 +765,7 @@ def run_resnet(args):
             "exact_images_per_s": round(e["images_per_s_per_gpu"] * world, 1),
             "ratio_to_exact": round(q["images_per_s_per_gpu"] / e["images_per_s_per_gpu"], 4),
             "activation_bytes": q["activation_bytes"], "exact_activation_bytes": e["activation_bytes"],
+            "peak_bytes": q["peak_bytes"], "exact_peak_bytes": e["peak_bytes"],
             "activation_reduction_vs_%s_autocast" % args.amp: round(e["activation_bytes"] / max(q["activation_bytes"], 1), 2),
             "exact_float32_activation_bytes": fp32_act,
             "activation_reduction_vs_float32": None if not fp32_act else round(fp32_act / max(q["activation_bytes"], 1), 2),
