@@ -19,44 +19,12 @@ LIB_PATH = os.environ.get("ACTNN_B200_LIB") or os.path.join(_HERE, "csrc", "liba
 F32, F16, BF16 = 0, 1, 2
 _DTYPE_ID = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
-_P, _I, _L, _U, _F, _D = c_void_p, c_int, c_int64, c_uint64, c_float, c_double
+_CTYPES = {"P": c_void_p, "I": c_int, "L": c_int64, "U": c_uint64, "F": c_float, "D": c_double}
 
-# name -> argument types, exactly as declared in include/actnn_b200.h
-SIGNATURES = {
-    "actnn_minimax": [_P, _P, _P, _L, _L, _I, _P],
-    "actnn_bits_prefix": [_P, _L, _L, _L, _P, _P],
-    "actnn_pack_mixed": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _P, _U, _U, _P],
-    "actnn_unpack_mixed": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _P],
-    "actnn_pack_single": [_P, _P, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I, _I, _P, _U, _U, _P],
-    "actnn_unpack_single": [_P, _I, _P, _P, _P, _L, _L, _L, _I, _I, _P],
-    "actnn_compress_single": [_P, _I, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _P, _U, _U, _P],
-    "actnn_compress_mixed": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _I, _F, _F, _P, _I, _D, _I, _P,
-                             _U, _U, _P],
-    "actnn_compress_mixed_static": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _F, _F, _P, _I, _D, _I, _P, _U,
-                                    _U, _P],
-    "actnn_compress_mixed_prestat": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _F, _F, _P, _I, _D, _I,
-                                     _P, _U, _U, _P],
-    "actnn_batch_norm_stats_minimax": [_P] * 9 + [_L, _L, _L, _D, _D, _I, _P, _L, _P],
-    "actnn_range_sqr": [_P, _P, _L, _L, _I, _F, _F, _P, _P, _P],
-    "actnn_sample_sumsq": [_P, _P, _L, _L, _I, _P],
-    "actnn_calc_precision": [_P, _P, _L, _I, _D, _P, _P, _L, _L, _P, _L, _P],
-    "actnn_relu_forward": [_P, _P, _P, _L, _I, _P],
-    "actnn_relu_backward": [_P, _P, _P, _L, _I, _P],
-    "actnn_dropout_forward": [_P, _P, _P, _L, _F, _I, _P, _U, _U, _P],
-    "actnn_dropout_backward": [_P, _P, _P, _L, _F, _I, _P],
-    "actnn_dropout_uniform_fill": [_P, _L, _U, _U, _P],
-    "actnn_max_pool2d_forward": [_P, _P, _P, _L, _L, _L, _L] + [_I] * 9 + [_P],
-    "actnn_max_pool2d_backward": [_P, _P, _P, _L, _L, _L, _L] + [_I] * 9 + [_P],
-    "actnn_noise_fill": [_P, _L, _I, _U, _U, _P],
-    "actnn_bulk_wait_failures": [_P],
-    "actnn_bad_width_bundles": [_P],
-    "actnn_batch_norm_stats": [_P, _P, _P, _L, _L, _L, _D, _I, _P, _L, _P],
-    "actnn_batch_norm_elemt": [_P] * 6 + [_L, _L, _L, _I, _P, _L, _P],
-    "actnn_batch_norm_backward_reduce": [_P] * 8 + [_L, _L, _L, _I, _P, _L, _P],
-    "actnn_batch_norm_backward_elemt": [_P] * 8 + [_L, _P, _L, _L, _L, _I, _P, _L, _P],
-    "actnn_batch_norm_forward": [_P] * 8 + [_L, _L, _L, _D, _D, _I, _P, _L, _P],
-    "actnn_batch_norm_backward": [_P] * 8 + [_L, _L, _L, _I, _P, _L, _P],
-}
+from ._signatures import SIGNATURES as _LETTERS  # noqa: E402
+
+# name -> ctypes argument types, exactly as declared in include/actnn_b200.h
+SIGNATURES = {name: [_CTYPES[c] for c in letters] for name, letters in _LETTERS.items()}
 
 _lib = None
 
@@ -144,13 +112,33 @@ def scratch(device: torch.device, nbytes: int) -> torch.Tensor:
 
 
 _fns = {}
+_fast = None
+FAST_PATH = os.path.join(_HERE, "csrc", "_actnn_fastcall.so")
+
+
+def _fast_module():
+    """The generated CPython wrappers of the entry points (same library underneath, an order of
+    magnitude less marshalling than ctypes); ``False`` when they were not built or another build
+    of the library was requested."""
+    global _fast
+    if _fast is None:
+        _fast = False
+        if not os.environ.get("ACTNN_B200_LIB") and os.path.exists(FAST_PATH):
+            import importlib.util
+            load()                                            # libactnn_b200.so first: the wrappers link to it
+            spec = importlib.util.spec_from_file_location("_actnn_fastcall", FAST_PATH)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            _fast = mod
+    return _fast
 
 
 def call(name: str, tensor_for_device: torch.Tensor, *args) -> None:
     """Invoke ``name`` with the tensor's device current and check the status."""
     fn = _fns.get(name)
     if fn is None:
-        fn = _fns[name] = getattr(load(), name)
+        fast = _fast_module()
+        fn = _fns[name] = getattr(fast, name) if fast else getattr(load(), name)
     idx = tensor_for_device.device.index
     if idx is not None and idx != torch.cuda.current_device():
         with torch.cuda.device(idx):

@@ -575,8 +575,8 @@ def run_ours(args):
                        "ms_per_replay_min": round(min(replay_ms), 4), "ms_per_replay_max": round(max(replay_ms), 4),
                        "value_from": "median replay of the K-step CUDA graph, max over ranks per replay"},
             "e2e": e2e,
-            "gpu_launches": 5 * args.steps,
-            "launch_mode": "the K steps replayed from one CUDA graph; 4 kernels per compress, 1 per decompress",
+            "gpu_launches": 4 * args.steps,
+            "launch_mode": "the K steps replayed from one CUDA graph; 3 kernels per compress (group min / max, width allocation, pack), 1 per decompress",
             "roofline": dict(roof, peak=peak, peak_source=peak_src) if roof else None,
             "kernels": kernels,
             "resnet50_l3": resnet,

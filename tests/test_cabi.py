@@ -139,3 +139,20 @@ def test_host_code_past_validation_returns_without_a_gpu(lib):
     assert lib.actnn_minimax(256, 256, 256, 8, 256, 1, None) == LAUNCH
     args = [256] * 8 + [1 << 20, 4, 32, 256, 1, 1, 1.0, 1.0, None, 8, 8.0, 1, None, 0, 0, None]
     assert lib.actnn_compress_mixed(*args) == LAUNCH
+
+
+def test_fast_binding_exports_every_entry_point_and_validates_like_ctypes(lib):
+    """The generated CPython wrappers (csrc/_actnn_fastcall.so) are the binding the package calls
+    through; they must carry every entry point of the signature table and hand arguments over
+    unchanged (checked on calls that return from host-side validation, so without a GPU)."""
+    from actnn_b200 import _lib
+    fast = _lib._fast_module()
+    assert fast, "fast binding was not built"
+    for name, letters in _lib._LETTERS.items():
+        assert hasattr(fast, name), name
+    assert fast.actnn_minimax(None, None, None, 4, 30, 0, None) == lib.actnn_minimax(None, None, None, 4, 30, 0, None) != 0
+    assert fast.actnn_minimax(None, None, None, 0, 256, 0, None) == 0
+    with pytest.raises(TypeError):
+        fast.actnn_minimax(None, None, None, 0, 256, 0)
+    with pytest.raises(TypeError):
+        fast.actnn_minimax(None, None, None, 0.5, 256, 0, None)
