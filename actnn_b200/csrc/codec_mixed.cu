@@ -498,6 +498,56 @@ unpack_mixed_kernel(const int32_t* __restrict__ packed, const int32_t* __restric
   }
 }
 
+// How the flat unpack kernel deals out its tasks (32 consecutive groups each).  Block b owns tasks
+// b, b + gridDim.x, b + 2 gridDim.x, ... -- a sample is 20 to 30 consecutive tasks, so every block
+// meets every width in the proportion of the whole activation -- and its warps claim them one at
+// a time from a counter in shared memory: a warp that met wider (slower) samples simply takes
+// fewer tasks.  The last `split` tasks of a block are claimed as halves of 16 groups, which
+// shortens the ragged end of the launch (an activation is only a few tasks per resident warp).
+// Nothing is shared between blocks or launches.
+#ifndef ACTNN_UNPACK_SPLIT
+#define ACTNN_UNPACK_SPLIT 8
+#endif
+struct FlatClaim { int64_t task; int kb, ke; };            // bundles kb .. ke-1 of the task
+struct FlatPool {
+  unsigned* counters;                                      // [0] whole tasks claimed, [1] halves claimed
+  unsigned whole, halves;
+  bool in_halves;
+  ACTNN_DEV void init(unsigned* smem2, int64_t tasks, int split_tasks) {
+    counters = smem2;
+    const int64_t mine = tasks > blockIdx.x ? (tasks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t split = mine < split_tasks ? mine : split_tasks;
+    whole = (unsigned)(mine - split);
+    halves = (unsigned)(2 * split);
+    in_halves = false;
+    if (threadIdx.x < 2) counters[threadIdx.x] = 0u;
+    __syncthreads();
+  }
+  ACTNN_DEV int64_t task_of(unsigned i) const { return blockIdx.x + (int64_t)i * gridDim.x; }
+  ACTNN_DEV bool claim(int lane, FlatClaim& c) {
+    unsigned i = 0u;
+    if (!in_halves) {
+      if (lane == 0) i = atomicAdd(&counters[0], 1u);
+      i = __shfl_sync(kFull, i, 0);
+      if (i < whole) { c.task = task_of(i); c.kb = 0; c.ke = kFlatGroups / kFlatBundle; return true; }
+      in_halves = true;
+    }
+    if (lane == 0) i = atomicAdd(&counters[1], 1u);
+    i = __shfl_sync(kFull, i, 0);
+    if (i >= halves) return false;
+    constexpr int kHalfBundles = kFlatGroups / kFlatBundle / 2;
+    c.task = task_of(whole + (i >> 1));
+    c.kb = (int)(i & 1u) * kHalfBundles;
+    c.ke = c.kb + kHalfBundles;
+    return true;
+  }
+};
+// (sample, group) of group q; one 32-bit division where the activation allows it
+ACTNN_DEV void split_group_index(int64_t q, int64_t G, int64_t& n, int64_t& r) {
+  if (((uint64_t)q | (uint64_t)G) >> 32) { n = q / G; } else { n = (int64_t)((uint32_t)q / (uint32_t)G); }
+  r = q - n * G;
+}
+
 // ---------------------------------------------------------------------------- unpack, flat tasks
 // Same task shape as the flat pack: lane l owns group q0 + l of a task of 32 groups (its
 // sample, width, stream position, scale and min come from coalesced loads), and eight bundles
@@ -656,26 +706,22 @@ unpack_mixed_flat_kernel(const int32_t* __restrict__ packed, const int32_t* __re
                          const int64_t* __restrict__ word_offsets, const ST* __restrict__ scale,
                          const ST* __restrict__ mn, T* __restrict__ out, int64_t Q, int64_t G) {
   const int lane = threadIdx.x & 31;
-  const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const TransposePlan plan = make_transpose_plan(lane);
-  const int64_t tasks = (Q + kFlatGroups - 1) / kFlatGroups;
-  if (warp >= tasks) return;
-  int64_t q0 = warp * kFlatGroups;
-  int64_t n0 = q0 / G;
-  int64_t r0 = q0 - n0 * G;
-  const int64_t stride = nwarps * kFlatGroups;
-  const int64_t step_n = stride / G, step_r = stride - step_n * G;
+  __shared__ unsigned pool_counters[2];
+  FlatPool pool;
+  pool.init(pool_counters, (Q + kFlatGroups - 1) / kFlatGroups, ACTNN_UNPACK_SPLIT);
 
-  for (; q0 < Q; q0 += stride) {
+  FlatClaim claim;
+  while (pool.claim(lane, claim)) {
+    const int64_t q0 = claim.task * kFlatGroups;
     const int64_t q = q0 + lane;
-    int64_t n = n0, r = r0 + lane;
-    if (r >= G) { r -= G; ++n; }
     int b_l = -1;                                             // past the end of the activation
     int64_t off_l = 0;
     float sc_l = 1.f, m_l = 0.f;
     uint32_t t01_l = 0u, t23_l = 0u;
     if (q < Q) {
+      int64_t n, r;
+      split_group_index(q, G, n, r);
       b_l = __ldg(bits + n);
       if (b_l < 1 || b_l > 8) b_l = 0;                        // not a width: the pack kernel wrote nothing either
       off_l = __ldg(word_offsets + n) + r * (8 * b_l);
@@ -692,14 +738,14 @@ unpack_mixed_flat_kernel(const int32_t* __restrict__ packed, const int32_t* __re
         }
       }
     }
-    int k = 0;
-    while (k < kFlatGroups / kFlatBundle) {
+    int k = claim.kb;
+    while (k < claim.ke) {
       const int first = k * kFlatBundle;
       const int b = __shfl_sync(kFull, b_l, first);
       if (b < 0) break;
       const unsigned same = __ballot_sync(kFull, b_l == b) >> first;          // bit i: lane first + i
       const int run_lanes = same == 0xffffffffu >> first ? 32 - first : __ffs((int)~same) - 1;
-      const int k1 = k + run_lanes / kFlatBundle;
+      const int k1 = min(k + run_lanes / kFlatBundle, claim.ke);
       const uint32_t olo = __shfl_sync(kFull, (uint32_t)off_l, first);
       const uint32_t ohi = __shfl_sync(kFull, (uint32_t)((uint64_t)off_l >> 32), first);
       const int32_t* in = packed + (int64_t)(((uint64_t)ohi << 32) | olo) + lane;
@@ -713,9 +759,6 @@ unpack_mixed_flat_kernel(const int32_t* __restrict__ packed, const int32_t* __re
 #undef ACTNN_CASE
       k = k1;
     }
-    n0 += step_n;
-    r0 += step_r;
-    if (r0 >= G) { r0 -= G; ++n0; }
   }
 }
 
@@ -816,7 +859,8 @@ int launch_unpack(const int32_t* packed, const int32_t* bits, const int64_t* wor
   if (G % kFlatBundle == 0 && G >= kFlatGroups) {
     auto kernel = unpack_mixed_flat_kernel<T, ST>;
     const int64_t flat_tasks = (N * G + kFlatGroups - 1) / kFlatGroups;
-    kernel<<<persistent_grid(kernel, kThreads, flat_tasks), kThreads, 0, stream>>>(
+    // sized by half tasks: a small activation spreads over twice the warps (see FlatPool)
+    kernel<<<persistent_grid(kernel, kThreads, 2 * flat_tasks), kThreads, 0, stream>>>(
         packed, bits, word_offsets, (const ST*)scale, (const ST*)mn, (T*)out, N * G, G);
     return check_launch();
   }
