@@ -7,6 +7,8 @@
 // adds the gradients of those that selected it, in float32 and in a fixed order.  That
 // removes the reference's zero-fill and its atomicAdd scatter
 // (quantization_cuda_kernel.cu:712-733) and makes the result deterministic.
+#include <type_traits>
+
 #include "quant_math.cuh"
 
 namespace actnn {
@@ -97,11 +99,130 @@ max_pool_forward_fixed_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t
   }
 }
 
+template <typename T> ACTNN_DEV void oct_values(const Oct<T>& o, float (&f)[8]) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = o.f[j];
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if constexpr (std::is_same<T, __half>::value) {
+        f[2 * k] = __half2float(__ushort_as_half((unsigned short)(o.r[k] & 0xffffu)));
+        f[2 * k + 1] = __half2float(__ushort_as_half((unsigned short)(o.r[k] >> 16)));
+      } else {
+        f[2 * k] = __uint_as_float(o.r[k] << 16);
+        f[2 * k + 1] = __uint_as_float(o.r[k] & 0xffff0000u);
+      }
+    }
+  }
+}
+
+// Forward by output-row segments: K x K windows (K = 2 or 3), column stride 2, unit dilation,
+// column padding P = 0 or 1, rows of W % 8 == 0 elements in a vector-aligned tensor (the pooling
+// layers of the ResNets, VGGs and DenseNets).  A thread owns eight consecutive outputs of one
+// output row.  Their windows cover the 16 input columns 2 wo0 .. 2 wo0 + 15 plus at most one
+// column on either side, so a window row costs two vector loads and at most two scalar ones
+// instead of 8 K scalar loads.  A tap outside the plane counts as -inf: with the strict
+// comparison and the -inf start that is the same as skipping it.  Scan order, comparison and
+// codes are those of the general kernel.
+template <typename T, int K, int P>
+__global__ void __launch_bounds__(256)
+max_pool_forward_row_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t* __restrict__ idx,
+                            uint32_t total_segments, int segs_per_row, PoolGeom g, int vector_store) {
+  const int out_elems = g.Ho * g.Wo, plane_elems = g.H * g.W;
+  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < total_segments; t += gridDim.x * blockDim.x) {
+    const uint32_t row = t / (uint32_t)segs_per_row;
+    const int seg = (int)(t - row * (uint32_t)segs_per_row);
+    const uint32_t nc = row / (uint32_t)g.Ho;
+    const int ho = (int)(row - nc * (uint32_t)g.Ho);
+    const int wo0 = seg * 8, c0 = 2 * wo0;
+    const T* plane = x + (int64_t)nc * plane_elems;
+    const int hb = ho * g.SH - g.PH;
+    float best[8];
+    int arg[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { best[i] = -INFINITY; arg[i] = 0; }
+#pragma unroll
+    for (int kh = 0; kh < K; ++kh) {
+      const int h = hb + kh;
+      if (h < 0 || h >= g.H) continue;
+      const T* r = plane + h * g.W;
+      float v[18];                                               // v[j]: column c0 - 1 + j
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int cc = c0 + 8 * half;
+        float f[8];
+        if (cc + 8 <= g.W) {
+          oct_values<T>(load_oct<T>(r + cc), f);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = cc + j < g.W ? load_scalar<T>(r, cc + j) : -INFINITY;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[1 + 8 * half + j] = f[j];
+      }
+      v[0] = (P == 1 && c0 >= 1) ? load_scalar<T>(r, c0 - 1) : -INFINITY;
+      v[17] = (K - P == 3 && c0 + 16 < g.W) ? load_scalar<T>(r, c0 + 16) : -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+#pragma unroll
+        for (int kw = 0; kw < K; ++kw) {
+          const float val = v[2 * i - P + kw + 1];
+          if (val > best[i]) { best[i] = val; arg[i] = kh * K + kw; }
+        }
+      }
+    }
+    const int64_t o = (int64_t)nc * out_elems + ho * g.Wo + wo0;
+    if (vector_store) {                                          // Wo % 8 == 0, aligned outputs
+      Oct<T> out;
+      if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out.f[i] = best[i];
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          out.r[k] = bits_of<T>(best[2 * k]) | (bits_of<T>(best[2 * k + 1]) << 16);   // values of T: exact
+        }
+      }
+      store_oct<T>(y + o, out);
+      uint2 codes;
+      codes.x = (uint32_t)arg[0] | ((uint32_t)arg[1] << 8) | ((uint32_t)arg[2] << 16) | ((uint32_t)arg[3] << 24);
+      codes.y = (uint32_t)arg[4] | ((uint32_t)arg[5] << 8) | ((uint32_t)arg[6] << 16) | ((uint32_t)arg[7] << 24);
+      *reinterpret_cast<uint2*>(idx + o) = codes;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (wo0 + i < g.Wo) {
+          store_scalar<T>(y, o + i, best[i]);
+          idx[o + i] = (int8_t)arg[i];
+        }
+      }
+    }
+  }
+}
+
 template <typename T>
 int launch_forward(const void* x, void* y, int8_t* idx, int64_t planes, const PoolGeom& g, cudaStream_t s) {
   const int out_elems = g.Ho * g.Wo;
-  dim3 grid = plane_grid(out_elems, planes);
   const bool unit = g.DH == 1 && g.DW == 1 && g.KH == g.KW;
+  const int segs = (g.Wo + 7) / 8;
+  const int64_t total_segments = planes * g.Ho * segs;
+  if (unit && (g.KH == 2 || g.KH == 3) && g.SW == 2 && g.PW <= 1 && g.W % 8 == 0 && aligned(x, sizeof(T) * 8) &&
+      total_segments < ((int64_t)1 << 31)) {
+    const int vec = g.Wo % 8 == 0 && aligned(y, sizeof(T) * 8) && aligned(idx, 8);
+    const int64_t blocks = (total_segments + 255) / 256;
+    const int rgrid = (int)max((int64_t)1, min(blocks, (int64_t)device_info().sm_count * 16));
+#define ACTNN_ROW(K, P)                                                                                       \
+    max_pool_forward_row_kernel<T, K, P><<<rgrid, 256, 0, s>>>((const T*)x, (T*)y, idx, (uint32_t)total_segments, \
+                                                               segs, g, vec)
+    if (g.KH == 3 && g.PW == 1) ACTNN_ROW(3, 1);
+    else if (g.KH == 3) ACTNN_ROW(3, 0);
+    else if (g.PW == 1) ACTNN_ROW(2, 1);
+    else ACTNN_ROW(2, 0);
+#undef ACTNN_ROW
+    return check_launch();
+  }
+  dim3 grid = plane_grid(out_elems, planes);
   if (unit && g.KH == 3)
     max_pool_forward_fixed_kernel<T, 3><<<grid, 256, 0, s>>>((const T*)x, (T*)y, idx, (int)planes, g);
   else if (unit && g.KH == 2)
@@ -252,6 +373,119 @@ max_pool_backward_row_kernel(const T* __restrict__ gy, const int8_t* __restrict_
   }
 }
 
+// Backward by row segments for the geometries of the forward row kernel (K x K windows with
+// K = 2 or 3, stride 2, unit dilation, column padding P = 0 or 1, W % 8 == 0).  A thread owns
+// eight consecutive positions w0 .. w0 + 7 of one input row.  At most two window rows contain
+// the row, and the window columns that reach the segment are w0 / 2 + BLO .. w0 / 2 + BHI with
+// BLO = -1 for (K, P) = (3, 0), else 0, and BHI = 4 for P = 1, else 3: the four columns
+// w0 / 2 .. w0 / 2 + 3 come with one vector load of the codes and one of the gradients, the
+// fifth with a scalar load.  Window column b reaches the positions 2 b - P .. 2 b - P + K - 1 of
+// the segment, known at compile time.  Every position receives its terms in the general
+// kernel's order (window rows, then columns, ascending).
+template <typename T, int K, int P>
+__global__ void __launch_bounds__(256)
+max_pool_backward_s2_kernel(const T* __restrict__ gy, const int8_t* __restrict__ idx, T* __restrict__ gx,
+                            uint32_t total_segments, int segs_per_row, PoolGeom g, int vector_load) {
+  constexpr int BLO = (K == 3 && P == 0) ? -1 : 0, BHI = P == 1 ? 4 : 3, NB = BHI - BLO + 1;
+  const int out_elems = g.Ho * g.Wo, plane_elems = g.H * g.W;
+  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < total_segments; t += gridDim.x * blockDim.x) {
+    const uint32_t row = t / (uint32_t)segs_per_row;
+    const int seg = (int)(t - row * (uint32_t)segs_per_row);
+    const uint32_t nc = row / (uint32_t)g.H;
+    const int h = (int)(row - nc * (uint32_t)g.H);
+    const int w0 = seg * 8, b0 = seg * 4;
+    const T* gy_p = gy + (int64_t)nc * out_elems;
+    const int8_t* idx_p = idx + (int64_t)nc * out_elems;
+    const int ah = h + g.PH;
+    const int ho_hi = min(g.Ho - 1, ah / 2);
+    const int ho_lo = ah > K - 1 ? (ah - (K - 1) + 1) / 2 : 0;
+    int code[2][NB];
+    float grad[2][NB];
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const int base = min(ho_lo + a, g.Ho - 1) * g.Wo;
+      if (vector_load && b0 + 4 <= g.Wo) {
+        const uint32_t c4 = __ldg(reinterpret_cast<const uint32_t*>(idx_p + base + b0));
+        float f[4];
+        if constexpr (sizeof(T) == 4) {
+          const float4 v = __ldg(reinterpret_cast<const float4*>(gy_p + base + b0));
+          f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+        } else {
+          const uint2 v = __ldg(reinterpret_cast<const uint2*>(gy_p + base + b0));
+          const uint32_t r[2] = {v.x, v.y};
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            if constexpr (std::is_same<T, __half>::value) {
+              f[2 * k] = __half2float(__ushort_as_half((unsigned short)(r[k] & 0xffffu)));
+              f[2 * k + 1] = __half2float(__ushort_as_half((unsigned short)(r[k] >> 16)));
+            } else {
+              f[2 * k] = __uint_as_float(r[k] << 16);
+              f[2 * k + 1] = __uint_as_float(r[k] & 0xffff0000u);
+            }
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          code[a][b - BLO] = (int)((c4 >> (8 * b)) & 0xffu);
+          grad[a][b - BLO] = f[b];
+        }
+      } else {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int o = base + min(b0 + b, g.Wo - 1);
+          code[a][b - BLO] = idx_p[o];
+          grad[a][b - BLO] = load_scalar<T>(gy_p, o);
+        }
+      }
+      if constexpr (BLO < 0) {
+        const int o = base + max(b0 - 1, 0);
+        code[a][0] = idx_p[o];
+        grad[a][0] = load_scalar<T>(gy_p, o);
+      }
+      if constexpr (BHI > 3) {
+        const int o = base + min(b0 + 4, g.Wo - 1);
+        code[a][NB - 1] = idx_p[o];
+        grad[a][NB - 1] = load_scalar<T>(gy_p, o);
+      }
+    }
+    // Position j (column w0 + j) is tap (j + P) % 2 of window column (j + P) / 2 and, for K = 3 and
+    // an even j + P, also tap 2 of the column before: one or two candidates per window row, each
+    // a comparison of the stored code with the code that would name this position.
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const int ho = ho_lo + a;
+      const int first_code = ho <= ho_hi ? (ah - ho * 2) * K : -64;   // code of tap column 0 in this input row
+#pragma unroll
+      for (int bi = 0; bi < NB; ++bi) {
+        const int wo = b0 + bi + BLO;
+        if (wo < 0 || wo >= g.Wo) code[a][bi] = -1;                // a clamped load, not a window
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int q = j + P, b_hi = q >> 1, kw_hi = q & 1;         // compile-time after unrolling
+        if (K == 3 && kw_hi == 0 && b_hi - 1 >= BLO)
+          acc[j] += code[a][b_hi - 1 - BLO] == first_code + 2 ? grad[a][b_hi - 1 - BLO] : 0.f;
+        if (b_hi <= BHI)
+          acc[j] += code[a][b_hi - BLO] == first_code + kw_hi ? grad[a][b_hi - BLO] : 0.f;
+      }
+    }
+    Oct<T> out;
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) out.f[j] = acc[j];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        out.r[k] = bits_of<T>(round_to<T>(acc[2 * k])) | (bits_of<T>(round_to<T>(acc[2 * k + 1])) << 16);
+      }
+    }
+    store_oct<T>(gx + (int64_t)nc * plane_elems + h * g.W + w0, out);
+  }
+}
+
 template <typename T>
 int launch_backward(const void* gy, const int8_t* idx, void* gx, int64_t planes, const PoolGeom& g, cudaStream_t s) {
   const int plane_elems = g.H * g.W;
@@ -262,6 +496,21 @@ int launch_backward(const void* gy, const int8_t* idx, void* gx, int64_t planes,
   const int nwin = (7 + g.KW - 1) / g.SW + 1;
   const int segs = (g.W + 7) / 8;
   const int64_t total_segments = planes * g.H * segs;
+  if (unit && g.KH == g.KW && (g.KH == 2 || g.KH == 3) && g.SH == 2 && g.SW == 2 && g.PW <= 1 && g.W % 8 == 0 &&
+      aligned(gx, sizeof(T) * 8) && total_segments < ((int64_t)1 << 31)) {
+    const int vec = g.Wo % 4 == 0 && aligned(gy, sizeof(T) * 4) && aligned(idx, 4);
+    const int64_t blocks = (total_segments + 255) / 256;
+    const int grid = (int)max((int64_t)1, min(blocks, (int64_t)device_info().sm_count * 16));
+#define ACTNN_S2(K, P)                                                                                      \
+    max_pool_backward_s2_kernel<T, K, P><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, (uint32_t)total_segments, \
+                                                              segs, g, vec)
+    if (g.KH == 3 && g.PW == 1) ACTNN_S2(3, 1);
+    else if (g.KH == 3) ACTNN_S2(3, 0);
+    else if (g.PW == 1) ACTNN_S2(2, 1);
+    else ACTNN_S2(2, 0);
+#undef ACTNN_S2
+    return check_launch();
+  }
   if (unit && (g.KH + g.SH - 1) / g.SH <= 2 && nwin <= 10 && total_segments < ((int64_t)1 << 31)) {
     uint64_t kh_of = 0, kw_of = 0;                               // code -> (kh, kw), one nibble each
     for (int c = 0; c < g.KH * g.KW; ++c) {

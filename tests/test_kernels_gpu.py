@@ -293,7 +293,16 @@ def test_dropout_forward_backward(ext, dtype):
                                   ((2, 2, 15, 15), (3, 3), (2, 2), (1, 1), (2, 2)),
                                   ((2, 4, 16, 32), (3, 3), (2, 2), (1, 1), (1, 1)),     # vector stores
                                   ((2, 2, 16, 16), (2, 2), (1, 1), (0, 0), (1, 1)),     # stride 1: ten columns
-                                  ((1, 3, 9, 40), (2, 3), (2, 3), (1, 1), (1, 1))])
+                                  ((1, 3, 9, 40), (2, 3), (2, 3), (1, 1), (1, 1)),
+                                  # rows of W % 8 == 0, stride 2: the row-segment kernels, every (K, P) variant,
+                                  # vector and scalar loads / stores, window columns that leave the plane
+                                  ((2, 3, 14, 32), (3, 3), (2, 2), (0, 0), (1, 1)),
+                                  ((2, 3, 16, 24), (3, 3), (2, 2), (1, 1), (1, 1)),
+                                  ((2, 3, 10, 32), (2, 2), (2, 2), (0, 0), (1, 1)),
+                                  ((2, 3, 10, 16), (2, 2), (2, 2), (1, 1), (1, 1)),
+                                  ((1, 2, 11, 40), (3, 3), (2, 2), (0, 1), (1, 1)),
+                                  ((1, 2, 12, 8), (3, 3), (2, 2), (1, 0), (1, 1)),
+                                  ((3, 5, 8, 8), (2, 2), (2, 2), (0, 1), (1, 1))])
 def test_max_pool2d_forward_backward(ext, dtype, geom):
     shape, k, s, p, d = geom
     x = make_input(shape, dtype, sum(shape))
