@@ -311,12 +311,12 @@ def kernel_table(torch, lib, _lib, quantization, dev, args, xs, packed, scales, 
     torch.cuda.empty_cache()
 
     # ---- roofline: the kernel of the timed step that sits furthest below the copy peak
-    name, ent = min((("pack_mixed_kernel<bfloat16> (inside actnn_compress_mixed)", e_pack),
-                     ("unpack_mixed_kernel<bfloat16> (actnn_unpack_mixed)", e_unpack)), key=lambda t: t[1]["frac"])
+    name, ent = min((("pack_mixed_flat_kernel<bfloat16> (inside actnn_compress_mixed)", e_pack),
+                     ("unpack_mixed_flat_kernel<bfloat16> (actnn_unpack_mixed)", e_unpack)), key=lambda t: t[1]["frac"])
     traffic, traffic_src = None, None
     tpath = os.path.join(ROOT, "profiles", "roofline_traffic.json")
     if os.path.exists(tpath):
-        key = "pack_mixed_bf16_bytes_per_launch" if "pack" in name else "unpack_mixed_bf16_bytes_per_launch"
+        key = ("pack" if name.startswith("pack") else "unpack") + "_mixed_bf16_bytes_per_launch"
         traffic = json.load(open(tpath)).get(key)
         traffic_src = "static figure from an ncu capture (profiles/roofline_traffic.json), not measured in this run"
     roof = {"kernel": name, "bound": "hbm", "achieved": ent["gbs"], "unit": "GB/s", "frac": ent["frac"],
