@@ -113,9 +113,17 @@ ACTNN_DEV void range_sqr_block(const ST* __restrict__ mn, const ST* __restrict__
   const int64_t n = first_sample + sub;
   if (n < N) {
     float acc = 0.f;
-    for (int64_t g = t; g < G; g += kThreads) {
-      const float d = round_to<ST>(__fsub_rn(load_scalar<ST>(mx, n * G + g), load_scalar<ST>(mn, n * G + g)));
-      acc = __fmaf_rn(d, d, acc);
+    // four groups per trip so that their loads travel together; a group past the end adds
+    // fma(0, 0, acc) = acc, and the order of the additions stays g ascending
+    for (int64_t g0 = t; g0 < G; g0 += 4 * kThreads) {
+      float d[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t g = g0 + u * kThreads;
+        d[u] = g < G ? round_to<ST>(__fsub_rn(load_scalar<ST>(mx, n * G + g), load_scalar<ST>(mn, n * G + g))) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc = __fmaf_rn(d[u], d[u], acc);
     }
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(kFull, acc, s);

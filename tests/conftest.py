@@ -56,3 +56,23 @@ def built_library():
     if os.path.exists(lib_build.NVCC) or shutil.which("nvcc"):
         lib_build.build()
     return lib_build.LIB
+
+
+@pytest.fixture(autouse=True)
+def fresh_scheme_registry():
+    """The package keeps process-wide state the way the reference does (the configuration object
+    and the list of every scheme ever created, which the per-layer allocation walks).  Every test
+    starts from and leaves an empty registry and the default configuration, whatever ran before."""
+    import actnn_b200
+    from actnn_b200.conf import QuantizationConfig
+
+    def reset():
+        actnn_b200.config.__dict__.update(QuantizationConfig().__dict__)
+        actnn_b200.QScheme.layers.clear()
+        actnn_b200.QBNScheme.layers.clear()
+        actnn_b200.QScheme.num_layers = 0
+        actnn_b200.QScheme.prev_layer = None
+
+    reset()
+    yield
+    reset()

@@ -29,6 +29,7 @@ def actnn(cuda_device):
 
 
 def philox_state():
+    torch.cuda.init()                                   # the generators exist only once CUDA is up
     gen = torch.cuda.default_generators[torch.cuda.current_device()]
     return gen.initial_seed(), gen.get_offset()
 
