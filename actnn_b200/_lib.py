@@ -149,6 +149,29 @@ def call(name: str, tensor_for_device: torch.Tensor, *args) -> None:
         check(status, name)
 
 
+_staged_failures_seen = 0
+
+
+def check_staged_pack(tensor: torch.Tensor, name: str) -> None:
+    """With the opt-in staged single-stream pack (``ACTNN_STAGED_PACK=1``) a warp whose bounded
+    wait for a bulk copy runs out leaves its part of the outputs unwritten and counts the event on
+    the device.  The library call itself cannot know (it only enqueues), so the binding waits for
+    the stream and reads the counter: a give-up becomes an error here instead of a silently
+    corrupted activation.  The default pack has no waits and is not checked."""
+    global _staged_failures_seen
+    if os.environ.get("ACTNN_STAGED_PACK", "0") in ("", "0"):
+        return
+    import ctypes
+    torch.cuda.current_stream(tensor.device).synchronize()
+    count = ctypes.c_uint32(0)
+    call("actnn_bulk_wait_failures", tensor, ctypes.addressof(count))
+    if count.value > _staged_failures_seen:
+        new = count.value - _staged_failures_seen
+        _staged_failures_seen = count.value
+        raise RuntimeError("%s: %d warps of the staged pack gave up waiting for a bulk copy; the packed "
+                           "output is incomplete" % (name, new))
+
+
 def next_philox(device: torch.device):
     """(seed, offset) from torch's default CUDA generator of ``device``; advances the offset
     so that ``torch.manual_seed`` reproduces a whole run, as the reference does with

@@ -207,6 +207,7 @@ def pack_single_precision(data, min, max, bits, stochastic, *, noise=None, philo
     _lib.call("actnn_pack_single", data, data.data_ptr(), min.data_ptr(), max.data_ptr(), bits,
               packed.data_ptr(), scale.data_ptr(), _lib.ptr(mn_out), n, g, gs, _lib.dtype_id(data.dtype),
               _lib.dtype_id(sdt), int(bool(stochastic)), nz, seed, offset, _lib.stream_of(data))
+    _lib.check_staged_pack(data, "actnn_pack_single")
     if return_min:
         return packed, scale, mn_out
     return packed, scale
@@ -231,6 +232,7 @@ def compress_single_precision(data, bits, stochastic=True, *, noise=None, philox
     _lib.call("actnn_compress_single", data, data.data_ptr(), bits, packed.data_ptr(), scale.data_ptr(),
               mn.data_ptr(), _lib.ptr(mx), n, g, gs, _lib.dtype_id(data.dtype), _lib.dtype_id(sdt),
               int(bool(stochastic)), nz, seed, offset, _lib.stream_of(data))
+    _lib.check_staged_pack(data, "actnn_compress_single")
     if return_max:
         return packed, scale, mn, mx
     return packed, scale, mn

@@ -156,3 +156,35 @@ def test_fast_binding_exports_every_entry_point_and_validates_like_ctypes(lib):
         fast.actnn_minimax(None, None, None, 0, 256, 0)
     with pytest.raises(TypeError):
         fast.actnn_minimax(None, None, None, 0.5, 256, 0, None)
+
+
+def test_staged_pack_give_up_becomes_an_error(monkeypatch):
+    """The binding turns a non-zero wait-failure counter of the opt-in staged pack into an error
+    (host logic only: the library call and the stream are faked)."""
+    import torch
+    from actnn_b200 import _lib
+
+    class FakeStream:
+        def synchronize(self):
+            pass
+
+    counter = {"value": 0}
+
+    def fake_call(name, tensor, address):
+        assert name == "actnn_bulk_wait_failures"
+        ctypes.c_uint32.from_address(address).value = counter["value"]
+
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: FakeStream())
+    monkeypatch.setattr(_lib, "call", fake_call)
+    monkeypatch.setattr(_lib, "_staged_failures_seen", 0)
+    x = torch.zeros(1)
+    monkeypatch.delenv("ACTNN_STAGED_PACK", raising=False)
+    counter["value"] = 5
+    _lib.check_staged_pack(x, "actnn_pack_single")             # default pack: never checked
+    monkeypatch.setenv("ACTNN_STAGED_PACK", "1")
+    counter["value"] = 0
+    _lib.check_staged_pack(x, "actnn_pack_single")
+    counter["value"] = 3
+    with pytest.raises(RuntimeError, match="3 warps"):
+        _lib.check_staged_pack(x, "actnn_pack_single")
+    _lib.check_staged_pack(x, "actnn_pack_single")             # the same three are not reported twice
