@@ -423,8 +423,14 @@ ACTNN_DEV void unpack_bundle(const uint32_t (&words)[8], float stat_scale, float
         for (int j = 0; j < 8; ++j) v[j] = __shfl_sync(kFull, entry, base + (int)code[j]);
       } else {
         const float sc = __shfl_sync(kFull, stat_scale, gi), m = __shfl_sync(kFull, stat_mn, gi);
+        float y = 0.f;
+        if (sizeof(T) == 2 && group_reciprocal(sc, y)) {           // 16-bit statistics; warp-uniform
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = dequant_bits<T>((float)code[j], sc, m);
+          for (int j = 0; j < 8; ++j) v[j] = dequant_bits_recip<T>((float)code[j], sc, y, m);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = dequant_bits<T>((float)code[j], sc, m);
+        }
       }
       if constexpr (sizeof(T) == 4) {
 #pragma unroll
@@ -554,10 +560,16 @@ ACTNN_DEV void split_group_index(int64_t q, int64_t G, int64_t& n, int64_t& r) {
 // of four groups are decoded with the words of the next bundle already requested.  For 16-bit
 // outputs at 1 or 2 bits the lane also computes the 2^B decoded values of its own group once
 // per task (packed in two registers); a bundle then fetches them with two shuffles per group.
-template <typename T, int B>
+#ifndef ACTNN_UNPACK_DIRECT_FROM
+#define ACTNN_UNPACK_DIRECT_FROM 6
+#endif
+template <typename T, int B, bool FASTDIV>
 ACTNN_DEV void unpack_flat_bundle(const uint32_t (&words)[B], float sc_l, float m_l, uint32_t t01_l, uint32_t t23_l,
                                   int first, int64_t q, T* __restrict__ out, const TransposePlan& plan, int lane) {
-  constexpr int E = 1 << (B < 6 ? B : 5);              // table entries per group
+  // from kDirect bits on every element is computed (a table of 2^B entries no longer fits a warp,
+  // or costs more shuffles than the arithmetic)
+  constexpr int kDirect = FASTDIV ? ACTNN_UNPACK_DIRECT_FROM : 6;
+  constexpr int E = 1 << (B < kDirect ? B : 5);        // table entries per group
   constexpr int GPC = (32 / E) < kFlatBundle ? (32 / E) : kFlatBundle;   // groups served by one table
   constexpr bool PAIRS = sizeof(T) == 2 && B <= 2;
   uint32_t S[B];
@@ -566,7 +578,7 @@ ACTNN_DEV void unpack_flat_bundle(const uint32_t (&words)[B], float sc_l, float 
   uint32_t entry = 0u;
 #pragma unroll
   for (int gi = 0; gi < kFlatBundle; ++gi) {
-    if constexpr (!PAIRS && B < 6) {
+    if constexpr (!PAIRS && B < kDirect) {
       if (gi % GPC == 0) {                               // (re)build the table for groups gi .. gi+GPC-1
         const int g = first + ((gi + lane / E) & (kFlatBundle - 1));
         const float sc = __shfl_sync(kFull, sc_l, g), m = __shfl_sync(kFull, m_l, g);
@@ -595,14 +607,20 @@ ACTNN_DEV void unpack_flat_bundle(const uint32_t (&words)[B], float sc_l, float 
       const uint32_t S2[2] = {lo, hi};
       uint32_t code[8];
       get_codes<B, 0>(S2, code);
-      if constexpr (B < 6) {
+      if constexpr (B < kDirect) {
         const int base = (gi % GPC) * E;
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = __shfl_sync(kFull, entry, base + (int)code[j]);
       } else {
         const float sc = __shfl_sync(kFull, sc_l, first + gi), m = __shfl_sync(kFull, m_l, first + gi);
+        float y = 0.f;
+        if (FASTDIV && group_reciprocal(sc, y)) {                 // warp-uniform: one scale per group
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = dequant_bits<T>((float)code[j], sc, m);
+          for (int j = 0; j < 8; ++j) v[j] = dequant_bits_recip<T>((float)code[j], sc, y, m);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = dequant_bits<T>((float)code[j], sc, m);
+        }
       }
       if constexpr (sizeof(T) == 4) {
 #pragma unroll
@@ -619,7 +637,7 @@ ACTNN_DEV void unpack_flat_bundle(const uint32_t (&words)[B], float sc_l, float 
 // A run of bundles k0 .. k1-1 of one width B (see pack_flat_run): the B words per lane of
 // bundle k+1 are requested before bundle k is decoded.  `in` points at this lane's first word
 // of bundle k0; a bundle is 32 * B words.
-template <typename T, int B>
+template <typename T, int B, bool FASTDIV>
 ACTNN_DEV void unpack_flat_run(int k0, int k1, int64_t q0, const int32_t* __restrict__ in, float sc_l, float m_l,
                                uint32_t t01_l, uint32_t t23_l, T* __restrict__ out, const TransposePlan& plan,
                                int lane) {
@@ -690,10 +708,10 @@ ACTNN_DEV void unpack_flat_run(int k0, int k1, int64_t q0, const int32_t* __rest
     load(wa, in);
     for (int k = k0; k < k1; k += 2) {
       if (k + 1 < k1) load(wb, in + 32 * B);
-      unpack_flat_bundle<T, B>(wa, sc_l, m_l, t01_l, t23_l, k * kFlatBundle, q0 + k * kFlatBundle, out, plan, lane);
+      unpack_flat_bundle<T, B, FASTDIV>(wa, sc_l, m_l, t01_l, t23_l, k * kFlatBundle, q0 + k * kFlatBundle, out, plan, lane);
       if (k + 1 >= k1) break;
       if (k + 2 < k1) load(wa, in + 64 * B);
-      unpack_flat_bundle<T, B>(wb, sc_l, m_l, t01_l, t23_l, (k + 1) * kFlatBundle, q0 + (k + 1) * kFlatBundle, out,
+      unpack_flat_bundle<T, B, FASTDIV>(wb, sc_l, m_l, t01_l, t23_l, (k + 1) * kFlatBundle, q0 + (k + 1) * kFlatBundle, out,
                                plan, lane);
       in += 64 * B;
     }
@@ -750,7 +768,7 @@ unpack_mixed_flat_kernel(const int32_t* __restrict__ packed, const int32_t* __re
       const uint32_t ohi = __shfl_sync(kFull, (uint32_t)((uint64_t)off_l >> 32), first);
       const int32_t* in = packed + (int64_t)(((uint64_t)ohi << 32) | olo) + lane;
 #define ACTNN_CASE(B) \
-      case B: unpack_flat_run<T, B>(k, k1, q0, in, sc_l, m_l, t01_l, t23_l, out, plan, lane); break;
+      case B: unpack_flat_run<T, B, sizeof(ST) == 2>(k, k1, q0, in, sc_l, m_l, t01_l, t23_l, out, plan, lane); break;
       switch (b) {
         ACTNN_CASE(1) ACTNN_CASE(2) ACTNN_CASE(3) ACTNN_CASE(4) ACTNN_CASE(5) ACTNN_CASE(6) ACTNN_CASE(7)
         ACTNN_CASE(8)

@@ -323,11 +323,13 @@ unpack_single_kernel(const int8_t* __restrict__ packed, const ST* __restrict__ s
         } else {
           uint32_t v[8];
           const float sc_n = TABLE ? 0.f : __shfl_sync(kFull, sc, ni), m_n = TABLE ? 0.f : __shfl_sync(kFull, m, ni);
+          float y_n = 0.f;                                       // 16-bit statistics: one reciprocal per group
+          const bool recip = !TABLE && sizeof(ST) == 2 && group_reciprocal(sc_n, y_n);   // warp-uniform
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const uint32_t code = ((((j < 4) ? w.x : w.y) >> (8 * (j & 3))) >> (ni * BITS)) & (uint32_t)(E - 1);
             if constexpr (TABLE) v[j] = __shfl_sync(kFull, entry, ni * E + (int)code);
-            else v[j] = dequant_bits<T>((float)code, sc_n, m_n);
+            else v[j] = recip ? dequant_bits_recip<T>((float)code, sc_n, y_n, m_n) : dequant_bits<T>((float)code, sc_n, m_n);
           }
           if constexpr (sizeof(T) == 4) {
 #pragma unroll

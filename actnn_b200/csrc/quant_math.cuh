@@ -358,6 +358,25 @@ template <typename T> ACTNN_DEV uint32_t dequant_bits(float code, float scale, f
   return bits_of<T>(round_to<T>(__fadd_rn(q, mn)));
 }
 
+// The same for many codes of one group whose scale is a 16-bit value (float16 / bfloat16
+// statistics): the reciprocal is taken once per group and every element pays three fused
+// operations instead of an IEEE division,
+//     y = RN(1 / s),  q0 = RN(c y),  r = c - s q0 (exact in one FMA),  q = RN(q0 + r y),
+// which is the exactly rounded quotient RN(c / s) (Markstein's correction step).  Checked on the
+// CPU for every code 1..255 against every finite positive float16 scale and every bfloat16 scale
+// in [2^-60, 2^60]: no difference from the IEEE division.  `group_reciprocal` says whether a scale
+// is inside that range (anything else -- zero, infinity, NaN, negative, huge -- keeps the division).
+ACTNN_DEV bool group_reciprocal(float scale, float& y) {
+  y = __frcp_rn(scale);
+  return scale >= 8.673617379884035e-19f && scale <= 1.152921504606847e18f;   // [2^-60, 2^60]
+}
+template <typename T> ACTNN_DEV uint32_t dequant_bits_recip(float code, float scale, float y, float mn) {
+  const float q0 = __fmul_rn(code, y);
+  const float r = __fmaf_rn(-scale, q0, code);
+  const float q = round_to<T>(__fmaf_rn(r, y, q0));
+  return bits_of<T>(round_to<T>(__fadd_rn(q, mn)));
+}
+
 // ------------------------------------------------------------------ bit strings
 // A lane's slice of the packed stream is a little-endian bit string held in S[0..].
 template <int OFF, int NB> ACTNN_DEV void put_bits(uint32_t* S, uint32_t v) {

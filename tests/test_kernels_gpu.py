@@ -124,6 +124,52 @@ def test_mixed_precision_against_oracle(ext, dtype, n, g, stochastic):
         assert d2.dtype == torch.float32 and same_values(d2.cpu()[ok], od2[ok])
 
 
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("g", [32, 3])                 # flat tasks / bundle kernel
+def test_wide_widths_decode_like_the_division_for_any_scale(ext, dtype, g):
+    """From 6 bits on every element is computed: code / scale + min, each step rounded.  With
+    16-bit statistics the kernels take the reciprocal of a group's scale once and correct the
+    product with two fused multiply-adds (exactly rounded for scales in [2^-60, 2^60]); any other
+    scale -- zero, infinity, subnormal, huge -- must fall back to the division.  Random words,
+    random and hostile scales, against the oracle's dequantize."""
+    n = 12 if g == 32 else 6
+    gen = torch.Generator().manual_seed(11 * g)
+    bits = torch.tensor([6 + (i % 3) for i in range(n)], dtype=torch.int32)
+    words = O.mixed_total_words(bits, g, 256)
+    packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (words,), dtype=torch.int32, generator=gen)
+    stat = torch.bfloat16 if dtype == torch.float32 else dtype
+    scale = torch.exp(torch.randn(n, g, 1, generator=gen) * 3).to(stat)
+    hostile = [0.0, float("inf"), 1e-30, 6e-8, 5e4, 3e38, 1.0, 255.0]
+    for i, v in enumerate(hostile):
+        scale[i % n, (i * 5) % g, 0] = v
+    mn = torch.randn(n, g, 1, generator=gen).to(stat)
+    codes = O.unpack_mixed_layout(packed.numpy(), bits, n, g, 256)
+    want = O.dequantize(codes, scale.to(dtype) if dtype != torch.float32 else scale.float(),
+                        mn.to(dtype) if dtype != torch.float32 else mn.float())
+    got = ext.q.unpack_mixed_precision(dev(packed), dev(bits), dev(scale), dev(mn), n, g, 256,
+                                       **({"out_dtype": torch.float32} if dtype == torch.float32 else {}))
+    a, b = got.cpu().float(), want.float()
+    same = (a == b) | (torch.isnan(a) & torch.isnan(b))
+    assert bool(same.all()), (a[~same][:4], b[~same][:4])
+
+
+def test_eight_bit_single_stream_decodes_like_the_division(ext):
+    """The uniform 8-bit stream computes every element too (reciprocal + correction)."""
+    gen = torch.Generator().manual_seed(3)
+    n, g = 8, 6
+    for dtype in (torch.float16, torch.bfloat16):
+        packed = torch.randint(-128, 128, (n * g * 256,), dtype=torch.int8, generator=gen)
+        scale = torch.exp(torch.randn(n, g, 1, generator=gen) * 3).to(dtype)
+        scale[0, 0, 0], scale[1, 1, 0], scale[2, 2, 0] = 0.0, float("inf"), 6e-8
+        mn = torch.randn(n, g, 1, generator=gen).to(dtype)
+        codes = O.unpack_single_layout(packed.numpy(), 8, n, g, 256)
+        want = O.dequantize(codes, scale, mn)
+        got = ext.q.unpack_single_precision(dev(packed), 8, dev(scale), dev(mn), n, g, 256)
+        a, b = got.cpu().float(), want.float()
+        same = (a == b) | (torch.isnan(a) & torch.isnan(b))
+        assert bool(same.all()), (a[~same][:4], b[~same][:4])
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_constant_nonzero_group_decodes_to_its_value(ext, dtype):
     """(mx - mn) + 2e-6 rounds to zero for such a group in 16-bit types; the reference then
