@@ -150,7 +150,7 @@ class _QBatchNormMixin:
         """Momentum for the running statistics; also counts the batch (nn.BatchNorm semantics)."""
         factor = 0.0 if self.momentum is None else self.momentum
         if self.training and self.track_running_stats and self.num_batches_tracked is not None:
-            self.num_batches_tracked = self.num_batches_tracked + 1
+            self.num_batches_tracked.add_(1)          # in place, as nn.BatchNorm does: no buffer re-registration
             factor = 1.0 / float(self.num_batches_tracked) if self.momentum is None else self.momentum
         return factor
 

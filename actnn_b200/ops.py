@@ -14,6 +14,7 @@ reference; what changes is the codec underneath:
 * float32 inputs get their bfloat16 scale / min written by the pack kernel and read by the
   unpack kernel directly (the reference converts with extra kernels, ops.py:115-116,129-131).
 """
+import math
 from collections import namedtuple
 
 import numpy as np
@@ -76,7 +77,7 @@ def dequantize_and_unpack(data, shape, bits, scale, mn, out_dtype=None):
     if config.swap:
         data = swap_to_gpu(data)
     N = shape[0]
-    num_features = int(np.prod(shape[1:]))
+    num_features = math.prod(shape[1:])
     gs = config.group_size
     num_features = num_features + (gs - num_features % gs) % gs
     if isinstance(bits, int):
@@ -162,7 +163,7 @@ def dequantize_activation(quantized, q_input_shape, dtype=None):
         input = dequantize_and_unpack(q_input, q_input_shape, q_bits, q_scale, q_min, out_dtype=dtype)
 
     N = q_input_shape[0]
-    num_features = int(np.prod(q_input_shape[1:]))
+    num_features = math.prod(q_input_shape[1:])
     input = input.view(N, -1)[:, :num_features]
     return input.reshape(*q_input_shape).contiguous()
 

@@ -54,7 +54,7 @@ def compute_tensor_bytes(tensors) -> int:
     """Total bytes of the float32/int32/16-bit/int8 tensors in ``tensors`` (others count 0)."""
     if not isinstance(tensors, (list, tuple)):
         tensors = [tensors]
-    return int(sum(np.prod(t.size()) * _BYTES.get(t.dtype, 0) for t in tensors))
+    return int(sum(t.numel() * _BYTES.get(t.dtype, 0) for t in tensors))
 
 
 def empty_cache(ratio) -> None:
