@@ -125,6 +125,27 @@ def test_mixed_precision_against_oracle(ext, dtype, n, g, stochastic):
 
 
 @pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("n,g", [(1, 32), (3, 36), (7, 44), (5, 100), (40, 32), (2, 1000)])
+def test_flat_task_kernels_against_oracle(ext, dtype, n, g):
+    """Shapes with G % 4 == 0 and G >= 32 take the flat kernels (32-group tasks cut into runs of
+    one width, tasks claimed by the warps of a block, the last ones in halves): every width
+    1..8, tasks that end inside a bundle row of lanes, samples that change width inside a task,
+    fewer tasks than warps and more."""
+    x = make_input((n, g, 256), dtype, 7 * n + g, "scaled")
+    bits = torch.tensor([((3 * i) % 8) + 1 for i in range(n)], dtype=torch.int32)
+    mn, mx = O.group_minimax(x)
+    noise = O.torch_noise(x.shape, dtype, torch.Generator().manual_seed(g))
+    codes, oscale = O.quantize(x, bits, mn, mx, noise)
+    ok = torch.isfinite(oscale.float()).expand_as(x)
+    packed, scale = ext.q.pack_mixed_precision(dev(x), dev(mn), dev(mx), dev(bits), True, noise=dev(noise))
+    got = O.unpack_mixed_layout(packed.cpu().numpy(), bits, n, g, 256)
+    assert torch.equal(got[ok], codes[ok])
+    assert same_values(scale.cpu(), oscale)
+    deq = ext.q.unpack_mixed_precision(packed, dev(bits), scale, dev(mn), n, g, 256)
+    assert same_values(deq.cpu()[ok], O.dequantize(got, oscale, mn)[ok])
+
+
+@pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("g", [32, 3])                 # flat tasks / bundle kernel
 def test_wide_widths_decode_like_the_division_for_any_scale(ext, dtype, g):
     """From 6 bits on every element is computed: code / scale + min, each step rounded.  With
