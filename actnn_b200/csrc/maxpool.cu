@@ -142,27 +142,42 @@ max_pool_forward_row_kernel(const T* __restrict__ x, T* __restrict__ y, int8_t* 
     int arg[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { best[i] = -INFINITY; arg[i] = 0; }
+    // the loads of all K window rows are issued before the first comparison (rows outside the
+    // plane read a clamped row and are masked afterwards), so K times as many bytes are in flight
+    Oct<T> lo8[K], hi8[K];
+    float left[K], right[K];
+    const bool whole = c0 + 16 <= g.W;
+#pragma unroll
+    for (int kh = 0; kh < K; ++kh) {
+      const int h = min(max(hb + kh, 0), g.H - 1);
+      const T* r = plane + h * g.W;
+      if (whole) {
+        lo8[kh] = load_oct<T>(r + c0);
+        hi8[kh] = load_oct<T>(r + c0 + 8);
+      }
+      left[kh] = (P == 1 && c0 >= 1) ? load_scalar<T>(r, c0 - 1) : -INFINITY;
+      right[kh] = (K - P == 3 && c0 + 16 < g.W) ? load_scalar<T>(r, c0 + 16) : -INFINITY;
+    }
 #pragma unroll
     for (int kh = 0; kh < K; ++kh) {
       const int h = hb + kh;
       if (h < 0 || h >= g.H) continue;
-      const T* r = plane + h * g.W;
       float v[18];                                               // v[j]: column c0 - 1 + j
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int cc = c0 + 8 * half;
+      if (whole) {
         float f[8];
-        if (cc + 8 <= g.W) {
-          oct_values<T>(load_oct<T>(r + cc), f);
-        } else {
+        oct_values<T>(lo8[kh], f);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = cc + j < g.W ? load_scalar<T>(r, cc + j) : -INFINITY;
-        }
+        for (int j = 0; j < 8; ++j) v[1 + j] = f[j];
+        oct_values<T>(hi8[kh], f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[1 + 8 * half + j] = f[j];
+        for (int j = 0; j < 8; ++j) v[9 + j] = f[j];
+      } else {                                                   // the last segment of a row that is not a multiple of 16
+        const T* r = plane + h * g.W;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[1 + j] = c0 + j < g.W ? load_scalar<T>(r, c0 + j) : -INFINITY;
       }
-      v[0] = (P == 1 && c0 >= 1) ? load_scalar<T>(r, c0 - 1) : -INFINITY;
-      v[17] = (K - P == 3 && c0 + 16 < g.W) ? load_scalar<T>(r, c0 + 16) : -INFINITY;
+      v[0] = left[kh];
+      v[17] = right[kh];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
 #pragma unroll

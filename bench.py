@@ -855,6 +855,15 @@ def run_profile(args):
     calls["batch_norm_stats_minimax"] = lambda: lib.actnn_batch_norm_stats_minimax(
         x.data_ptr(), mn.data_ptr(), mx.data_ptr(), w.data_ptr(), bvec.data_ptr(), rm.data_ptr(), rv.data_ptr(),
         sm.data_ptr(), si.data_ptr(), N, bn_c, bn_hw, 0.1, 1e-5, F16, sm_ws.data_ptr(), sm_bytes, st)
+    # max pooling 3x3 / stride 2 / padding 1 (the ResNet stem) over the same bytes viewed as [128, 64, 112, 112]
+    pn, pc, ph, pw = 128, 64, 112, 112
+    py = torch.empty(pn, pc, ph // 2, pw // 2, dtype=dt, device=dev)
+    pidx = torch.empty(pn, pc, ph // 2, pw // 2, dtype=torch.int8, device=dev)
+    calls["max_pool_forward"] = lambda: lib.actnn_max_pool2d_forward(
+        x.data_ptr(), py.data_ptr(), pidx.data_ptr(), pn, pc, ph, pw, 3, 3, 2, 2, 1, 1, 1, 1, F16, st)
+    calls["max_pool_backward"] = lambda: lib.actnn_max_pool2d_backward(
+        py.data_ptr(), pidx.data_ptr(), out.data_ptr(), pn, pc, ph, pw, 3, 3, 2, 2, 1, 1, 1, 1, F16, st)
+    calls["max_pool_forward"]()
     calls["batch_norm_forward"]()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
