@@ -18,6 +18,20 @@ struct PoolGeom {
   int H, W, Ho, Wo, KH, KW, SH, SW, PH, PW, DH, DW;
 };
 
+// n / d for n < 2^31 with one multiply-high: the backward row kernel splits a flat segment index
+// into (plane, row, segment) with two of these instead of two 32-bit divisions.
+struct PoolDiv { uint32_t m, s; };
+PoolDiv make_pool_div(uint32_t d) {
+  PoolDiv f{0, 0};
+  if (d <= 1) return f;
+  uint32_t s = 0;
+  while (((uint64_t)1 << s) < d) ++s;
+  f.m = (uint32_t)((((uint64_t)1 << 32) * (((uint64_t)1 << s) - d)) / d + 1);
+  f.s = s;
+  return f;
+}
+ACTNN_DEV uint32_t pool_div(uint32_t n, const PoolDiv& f) { return (__umulhi(n, f.m) + n) >> f.s; }
+
 // Blocks are persistent: x covers a plane's positions (at most a few blocks), y strides over
 // the planes, and the whole grid is about 16 blocks per SM, so that the cost of launching
 // blocks does not dominate planes of a few thousand positions.
@@ -400,13 +414,14 @@ max_pool_backward_row_kernel(const T* __restrict__ gy, const int8_t* __restrict_
 template <typename T, int K, int P>
 __global__ void __launch_bounds__(256)
 max_pool_backward_s2_kernel(const T* __restrict__ gy, const int8_t* __restrict__ idx, T* __restrict__ gx,
-                            uint32_t total_segments, int segs_per_row, PoolGeom g, int vector_load) {
+                            uint32_t total_segments, int segs_per_row, PoolGeom g, int vector_load, PoolDiv by_segs,
+                            PoolDiv by_rows) {
   constexpr int BLO = (K == 3 && P == 0) ? -1 : 0, BHI = P == 1 ? 4 : 3, NB = BHI - BLO + 1;
   const int out_elems = g.Ho * g.Wo, plane_elems = g.H * g.W;
   for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < total_segments; t += gridDim.x * blockDim.x) {
-    const uint32_t row = t / (uint32_t)segs_per_row;
+    const uint32_t row = pool_div(t, by_segs);
     const int seg = (int)(t - row * (uint32_t)segs_per_row);
-    const uint32_t nc = row / (uint32_t)g.H;
+    const uint32_t nc = pool_div(row, by_rows);
     const int h = (int)(row - nc * (uint32_t)g.H);
     const int w0 = seg * 8, b0 = seg * 4;
     const T* gy_p = gy + (int64_t)nc * out_elems;
@@ -473,18 +488,22 @@ max_pool_backward_s2_kernel(const T* __restrict__ gy, const int8_t* __restrict__
     for (int a = 0; a < 2; ++a) {
       const int ho = ho_lo + a;
       const int first_code = ho <= ho_hi ? (ah - ho * 2) * K : -64;   // code of tap column 0 in this input row
+      if (b0 + BLO < 0 || b0 + BHI >= g.Wo) {                      // first / last segments of a row only
 #pragma unroll
-      for (int bi = 0; bi < NB; ++bi) {
-        const int wo = b0 + bi + BLO;
-        if (wo < 0 || wo >= g.Wo) code[a][bi] = -1;                // a clamped load, not a window
+        for (int bi = 0; bi < NB; ++bi) {
+          const int wo = b0 + bi + BLO;
+          if (wo < 0 || wo >= g.Wo) code[a][bi] = -1;              // a clamped load, not a window
+        }
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int q = j + P, b_hi = q >> 1, kw_hi = q & 1;         // compile-time after unrolling
-        if (K == 3 && kw_hi == 0 && b_hi - 1 >= BLO)
-          acc[j] += code[a][b_hi - 1 - BLO] == first_code + 2 ? grad[a][b_hi - 1 - BLO] : 0.f;
-        if (b_hi <= BHI)
-          acc[j] += code[a][b_hi - BLO] == first_code + kw_hi ? grad[a][b_hi - BLO] : 0.f;
+        if (K == 3 && kw_hi == 0 && b_hi - 1 >= BLO) {
+          if (code[a][b_hi - 1 - BLO] == first_code + 2) acc[j] += grad[a][b_hi - 1 - BLO];
+        }
+        if (b_hi <= BHI) {
+          if (code[a][b_hi - BLO] == first_code + kw_hi) acc[j] += grad[a][b_hi - BLO];
+        }
       }
     }
     Oct<T> out;
@@ -518,7 +537,8 @@ int launch_backward(const void* gy, const int8_t* idx, void* gx, int64_t planes,
     const int grid = (int)max((int64_t)1, min(blocks, (int64_t)device_info().sm_count * 16));
 #define ACTNN_S2(K, P)                                                                                      \
     max_pool_backward_s2_kernel<T, K, P><<<grid, 256, 0, s>>>((const T*)gy, idx, (T*)gx, (uint32_t)total_segments, \
-                                                              segs, g, vec)
+                                                              segs, g, vec, make_pool_div((uint32_t)segs),         \
+                                                              make_pool_div((uint32_t)g.H))
     if (g.KH == 3 && g.PW == 1) ACTNN_S2(3, 1);
     else if (g.KH == 3) ACTNN_S2(3, 0);
     else if (g.PW == 1) ACTNN_S2(2, 1);
