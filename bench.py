@@ -76,6 +76,24 @@ def synthetic_activation(torch, n, c, h, w, dtype, device, seed):
 # ---------------------------------------------------------------------------------------
 # multi-rank bookkeeping (one process per GPU; the codec itself needs no collective)
 # ---------------------------------------------------------------------------------------
+def init_nccl(dist, torch, dev):
+    """Join the NCCL group.  The library prints its version banner on stdout when its first
+    communicator is created; stdout carries exactly one JSON line, so file descriptor 1 points at
+    stderr until that has happened."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    try:
+        os.dup2(2, 1)
+        dist.init_process_group("nccl", device_id=dev)
+        warm = torch.zeros(1, device=dev)
+        dist.all_reduce(warm)
+        torch.cuda.synchronize()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 def max_over_ranks(local_ms: float, device=None) -> float:
     """The slowest rank's time: the whole job is as slow as its slowest replica."""
     import torch
@@ -446,7 +464,7 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        init_nccl(dist, torch, dev)
 
     N, C, H, W = WORKLOAD["shape"]
     gs, avg_bits, init_bits = 256, WORKLOAD["avg_bits"], WORKLOAD["initial_bits"]
@@ -737,7 +755,7 @@ def run_resnet(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        init_nccl(dist, torch, dev)
     steps, warm = max(3, min(args.steps, 30)), max(3, min(args.warmup, 5))
     if args.level in ("L4", "L5", "swap"):
         warm = max(warm, 8)          # the pinned pool of the host swap fills while the per-layer widths settle
