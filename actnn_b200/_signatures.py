@@ -25,6 +25,7 @@ SIGNATURES = {
     "actnn_sample_sumsq": ['P', 'P', 'L', 'L', 'I', 'P'],
     "actnn_calc_precision": ['P', 'P', 'L', 'I', 'D', 'P', 'P', 'L', 'L', 'P', 'L', 'P'],
     "actnn_relu_forward": ['P', 'P', 'P', 'L', 'I', 'P'],
+    "actnn_relu_forward_minimax": ['P', 'P', 'P', 'P', 'P', 'L', 'I', 'P'],
     "actnn_relu_backward": ['P', 'P', 'P', 'L', 'I', 'P'],
     "actnn_dropout_forward": ['P', 'P', 'P', 'L', 'F', 'I', 'P', 'U', 'U', 'P'],
     "actnn_dropout_backward": ['P', 'P', 'P', 'L', 'F', 'I', 'P'],

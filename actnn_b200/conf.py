@@ -20,6 +20,7 @@ class QuantizationConfig:
         self.group_size = 256
         self.use_gradient = False
         self.adaptive_conv_scheme = True
+        self.relu_minmax = True        # QReLU also produces the group ranges of its output (not in the reference)
         self.adaptive_bn_scheme = True
         self.simulate = False
         self.enable_quantized_bn = True

@@ -262,9 +262,18 @@ def noise_fill(numel: int, dtype: torch.dtype, device, seed: int, offset: int) -
 
 
 # ------------------------------------------------------------------------------- ReLU
-def relu_forward(x: torch.Tensor):
+def relu_forward(x: torch.Tensor, with_minmax: bool = False):
+    """``(y, mask)``; with ``with_minmax`` (``x.numel() % 256 == 0``) also the min and the max of
+    every 256 consecutive outputs, from the same pass: ``(y, mask, mn, mx)``."""
     y = torch.empty_like(x)
     mask = torch.empty((x.numel() + 31) // 32, dtype=torch.int32, device=x.device)
+    if with_minmax:
+        groups = x.numel() // 256
+        mn = torch.empty(groups, dtype=x.dtype, device=x.device)
+        mx = torch.empty(groups, dtype=x.dtype, device=x.device)
+        _lib.call("actnn_relu_forward_minimax", x, x.data_ptr(), y.data_ptr(), mask.data_ptr(), mn.data_ptr(),
+                  mx.data_ptr(), x.numel(), _lib.dtype_id(x.dtype), _lib.stream_of(x))
+        return y, mask, mn, mx
     _lib.call("actnn_relu_forward", x, x.data_ptr(), y.data_ptr(), mask.data_ptr(), x.numel(),
               _lib.dtype_id(x.dtype), _lib.stream_of(x))
     return y, mask
@@ -292,9 +301,39 @@ class _ActQuantizedReLU(torch.autograd.Function):
         return relu_backward(grad_output, mask)
 
 
+class _ActQuantizedReLUMinmax(torch.autograd.Function):
+    """The same op; the forward pass also returns the per-group extrema of its output."""
+
+    @staticmethod
+    def forward(ctx, x):
+        y, mask, mn, mx = relu_forward(x, with_minmax=True)
+        ctx.save_for_backward(mask)
+        ctx.mark_non_differentiable(mn, mx)
+        return y, mn, mx
+
+    @staticmethod
+    def backward(ctx, grad_output, _grad_mn, _grad_mx):
+        (mask,) = ctx.saved_tensors
+        return relu_backward(grad_output, mask)
+
+
 def act_quantized_relu(input: torch.Tensor) -> torch.Tensor:
     check_cuda_tensor(input, "input")
     return _ActQuantizedReLU.apply(input)
+
+
+def act_quantized_relu_with_minmax(input: torch.Tensor, group_size: int = 256):
+    """``act_quantized_relu`` that hands the next layer the ranges it would otherwise compute with
+    a pass of its own: the output carries ``(min, max)`` of every ``group_size`` consecutive
+    elements of each sample in ``output.actnn_minmax`` (with the tensor version they belong to).
+    Inputs whose samples are not whole groups of 256 contiguous elements take the plain op."""
+    check_cuda_tensor(input, "input")
+    n = input.shape[0] if input.dim() > 1 else 1
+    if group_size != 256 or n == 0 or (input.numel() // n) % 256 != 0 or not input.is_contiguous():
+        return _ActQuantizedReLU.apply(input)
+    y, mn, mx = _ActQuantizedReLUMinmax.apply(input)
+    y.actnn_minmax = (mn, mx, y._version)
+    return y
 
 
 # ------------------------------------------------------------------------------- dropout

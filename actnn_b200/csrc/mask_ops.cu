@@ -130,7 +130,8 @@ enum class Op { kReluFwd, kMaskBwd, kDropoutFwd };
 template <typename T, Op OP, bool FULL>
 ACTNN_DEV void mask_block(const T* __restrict__ in, T* __restrict__ out, int32_t* __restrict__ mask,
                           int64_t numel, int64_t mask_words, int64_t blk, int lane, float inv, float p,
-                          const float* __restrict__ u, const NoiseKey& key) {
+                          const float* __restrict__ u, const NoiseKey& key, T* __restrict__ group_mn = nullptr,
+                          T* __restrict__ group_mx = nullptr) {
   const int64_t e0 = blk * kBlockElems + lane * kOct;
   Oct<T> x[kRows];
   int valid[kRows];
@@ -173,6 +174,7 @@ ACTNN_DEV void mask_block(const T* __restrict__ in, T* __restrict__ out, int32_t
       keep |= kb << (8 * i);
     }
   }
+  float my_mn = 0.f, my_mx = 0.f;                     // lane i: extrema of output row i (ReLU with group_mn only)
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {
     if (!FULL && valid[i] == 0) continue;
@@ -181,6 +183,26 @@ ACTNN_DEV void mask_block(const T* __restrict__ in, T* __restrict__ out, int32_t
     const int64_t e = e0 + (int64_t)i * kGroup;
     if (FULL || valid[i] == kOct) store_oct<T>(out + e, y);
     else store_partial<T>(out + e, y, valid[i]);
+    if constexpr (OP == Op::kReluFwd) {
+      // the caller asked for the min / max of every 256 outputs (numel % 256 == 0, so a row is whole
+      // or absent for the entire warp): the same reduction as the minimax kernel, on y
+      if (group_mn) {
+        float lo, hi;
+        oct_minmax<T>(y, lo, hi);
+        lo = warp_min(lo);
+        hi = warp_max(hi);
+        if (lane == i) { my_mn = lo; my_mx = hi; }
+      }
+    }
+  }
+  if constexpr (OP == Op::kReluFwd) {
+    if (group_mn && lane < kRows) {
+      const int64_t g = blk * kRows + lane;
+      if (g * kGroup < numel) {
+        store_scalar<T>(group_mn, g, my_mn);
+        store_scalar<T>(group_mx, g, my_mx);
+      }
+    }
   }
   if constexpr (OP != Op::kMaskBwd) {
     // bits past numel are already zero: rows / elements beyond the end contribute 0
@@ -200,7 +222,8 @@ ACTNN_DEV void mask_block(const T* __restrict__ in, T* __restrict__ out, int32_t
 template <typename T, Op OP>
 __global__ void __launch_bounds__(kThreads)
 mask_kernel(const T* __restrict__ in, T* __restrict__ out, int32_t* __restrict__ mask, int64_t numel,
-            float inv, float p, const float* __restrict__ u, const NoiseKey key) {
+            float inv, float p, const float* __restrict__ u, const NoiseKey key, T* __restrict__ group_mn,
+            T* __restrict__ group_mx) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
@@ -208,8 +231,8 @@ mask_kernel(const T* __restrict__ in, T* __restrict__ out, int32_t* __restrict__
   const int64_t whole = numel / kBlockElems;            // blocks that lie wholly inside the tensor
   const int64_t mask_words = (numel + 31) / 32;
   for (int64_t blk = warp; blk < blocks; blk += nwarps) {
-    if (blk < whole) mask_block<T, OP, true>(in, out, mask, numel, mask_words, blk, lane, inv, p, u, key);
-    else mask_block<T, OP, false>(in, out, mask, numel, mask_words, blk, lane, inv, p, u, key);
+    if (blk < whole) mask_block<T, OP, true>(in, out, mask, numel, mask_words, blk, lane, inv, p, u, key, group_mn, group_mx);
+    else mask_block<T, OP, false>(in, out, mask, numel, mask_words, blk, lane, inv, p, u, key, group_mn, group_mx);
   }
 }
 
@@ -225,7 +248,8 @@ __global__ void dropout_uniform_kernel(float* __restrict__ u, int64_t numel, con
 
 template <Op OP>
 int launch(const void* in, void* out, int32_t* mask, int64_t numel, float inv, float p, const float* u,
-           uint64_t seed, uint64_t offset, int dtype, actnn_stream_t stream) {
+           uint64_t seed, uint64_t offset, int dtype, actnn_stream_t stream, void* group_mn = nullptr,
+           void* group_mx = nullptr) {
   if (numel < 0) return ACTNN_ERR_SHAPE;
   if (numel == 0) return ACTNN_OK;
   if (!in || !out || !mask) return ACTNN_ERR_NULL;
@@ -237,14 +261,17 @@ int launch(const void* in, void* out, int32_t* mask, int64_t numel, float inv, f
   const NoiseKey key = make_noise_key(seed, offset);
   switch (dtype) {
     case ACTNN_F32:
-      mask_kernel<float, OP><<<grid, kThreads, 0, s>>>((const float*)in, (float*)out, mask, numel, inv, p, u, key);
+      mask_kernel<float, OP><<<grid, kThreads, 0, s>>>((const float*)in, (float*)out, mask, numel, inv, p, u, key,
+                                                       (float*)group_mn, (float*)group_mx);
       break;
     case ACTNN_F16:
-      mask_kernel<__half, OP><<<grid, kThreads, 0, s>>>((const __half*)in, (__half*)out, mask, numel, inv, p, u, key);
+      mask_kernel<__half, OP><<<grid, kThreads, 0, s>>>((const __half*)in, (__half*)out, mask, numel, inv, p, u, key,
+                                                        (__half*)group_mn, (__half*)group_mx);
       break;
     case ACTNN_BF16:
       mask_kernel<__nv_bfloat16, OP><<<grid, kThreads, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, mask,
-                                                               numel, inv, p, u, key);
+                                                               numel, inv, p, u, key, (__nv_bfloat16*)group_mn,
+                                                               (__nv_bfloat16*)group_mx);
       break;
     default: return ACTNN_ERR_DTYPE;
   }
@@ -259,6 +286,13 @@ using namespace actnn;
 extern "C" int actnn_relu_forward(const void* x, void* y, int32_t* mask, int64_t numel, int dtype,
                                   actnn_stream_t stream) {
   return launch<Op::kReluFwd>(x, y, mask, numel, 1.f, 0.f, nullptr, 0, 0, dtype, stream);
+}
+
+extern "C" int actnn_relu_forward_minimax(const void* x, void* y, int32_t* mask, void* mn, void* mx, int64_t numel,
+                                          int dtype, actnn_stream_t stream) {
+  if (numel < 0 || numel % kGroup != 0) return ACTNN_ERR_SHAPE;
+  if (numel > 0 && (!mn || !mx)) return ACTNN_ERR_NULL;
+  return launch<Op::kReluFwd>(x, y, mask, numel, 1.f, 0.f, nullptr, 0, 0, dtype, stream, mn, mx);
 }
 
 extern "C" int actnn_relu_backward(const void* grad_out, const int32_t* mask, void* grad_in, int64_t numel,

@@ -219,6 +219,11 @@ class QReLU(nn.Module):
         super().__init__()
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
+        # the layer after a ReLU is nearly always a convolution that compresses this output: let
+        # the ReLU pass produce the group ranges that compression starts from
+        if (config.training and config.compress_activation and config.adaptive_conv_scheme and config.pergroup
+                and config.relu_minmax and not config.simulate):
+            return ext_quantization.act_quantized_relu_with_minmax(input, config.group_size)
         return ext_quantization.act_quantized_relu(input)
 
 

@@ -93,6 +93,19 @@ def no_scheme_compute_quantization_bits(input):
     return groups, config.activation_compression_bits[0], mn, mx
 
 
+def producer_minmax(input):
+    """Per-group extrema that the op which produced ``input`` left on it (QReLU does), if they still
+    describe it: same tensor version, contiguous, one value per 256 elements."""
+    rec = getattr(input, "actnn_minmax", None)
+    if rec is None:
+        return None
+    mn, mx, version = rec
+    if input._version != version or not input.is_contiguous() or mn.numel() * 256 != input.numel() \
+            or mn.dtype != input.dtype:
+        return None
+    return mn, mx
+
+
 def quantize_activation(input, scheme, minmax=None):
     """Compress one activation; returns ``(q_input, q_bits, q_scale, q_min)`` (ops.py:99-118).
 
@@ -214,7 +227,7 @@ class convnd(Function):
                     scheme=None):
         input, weight, bias = _autocast_inputs(input, weight, bias)
         with torch.autocast("cuda", enabled=False):
-            quantized = quantize_activation(input, scheme)
+            quantized = quantize_activation(input, scheme, minmax=producer_minmax(input) if scheme else None)
             ctx.scheme = scheme
             ctx.saved = quantized, weight, bias
             ctx.other_args = (input.shape, stride, padding, dilation, groups, input.dtype)

@@ -121,10 +121,12 @@ class QScheme(object):
         self.b = b
         return groups, b, mn, mx
 
-    def compress(self, input, stat_dtype):
-        """``compute_quantization_bits`` + mixed-precision pack as ONE native call (four kernel
+    def compress(self, input, stat_dtype, minmax=None):
+        """``compute_quantization_bits`` + mixed-precision pack as ONE native call (three kernel
         launches, no host synchronisation).  Returns ``(q_input, q_bits, q_scale, q_min)``, or
-        ``None`` when a configuration needs the step-by-step path."""
+        ``None`` when a configuration needs the step-by-step path.  ``minmax=(mn, mx)``: the
+        per-group extrema when the producer of ``input`` already has them (then the activation is
+        read once, not twice); only used when every sample is whole groups of 256."""
         grad = self.get_scale()
         if not config.pergroup or grad.numel() != 1:
             return None
@@ -134,10 +136,12 @@ class QScheme(object):
         if not grad.is_cuda or grad.dtype != torch.float32:
             grad = grad.to(device=input.device, dtype=torch.float32)
             self.scales = grad
+        if minmax is not None and (config.group_size != 256 or (input.numel() // N) % 256 != 0):
+            minmax = None                                      # padded groups: not the producer's
         q_input, b, q_scale, q_min, C = ext_quantization.compress_mixed_precision(
             to_groups(input), int(self.bits * N), int(self.initial_bits), config.group_size / num_pixels,
             self.num_locations / 4 / self.depthwise_groups, grad.reshape(1), config.stochastic,
-            stat_dtype=stat_dtype)
+            stat_dtype=stat_dtype, minmax=minmax)
         self.C = C
         self.dim = input.numel() // N
         self.b = b

@@ -261,6 +261,14 @@ int actnn_compress_mixed_prestat(const void* data, const void* mn, const void* m
  * actnn/actnn/cpp_extension/quantization.cc:106-124, quantization_cuda_kernel.cu:411-508. */
 int actnn_relu_forward(const void* x, void* y, int32_t* mask, int64_t numel, int dtype,
                        actnn_stream_t stream);
+
+/* The same pass, which also leaves the min and the max of every 256 consecutive OUTPUTS in mn[g] / mx[g]
+ * (g = element / 256; numel % 256 == 0), bit-identical to actnn_minimax(y).  The layer that consumes y
+ * (a convolution: actnn/actnn/ops.py:99-118 quantizes its input with QScheme.compute_quantization_bits,
+ * qscheme.py:57-94, whose first step is that min / max pass) can then compress it with
+ * actnn_compress_mixed_prestat, i.e. without reading y once more for the ranges. */
+int actnn_relu_forward_minimax(const void* x, void* y, int32_t* mask, void* mn, void* mx, int64_t numel,
+                               int dtype, actnn_stream_t stream);
 int actnn_relu_backward(const void* grad_out, const int32_t* mask, void* grad_in,
                         int64_t numel, int dtype, actnn_stream_t stream);
 

@@ -254,3 +254,66 @@ def test_a_layer_allocated_one_bit_still_compresses(actnn):
     assert torch.isfinite(y).all()
     groups, b, _, _ = layer.compute_quantization_bits(x)
     assert b.tolist() == [1] * 6
+
+
+# ------------------------------------------------------------------------------ ReLU that also yields the group ranges
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(6, 16, 16, 16), (3, 1024), (5, 256), (1, 2, 8, 16)])
+def test_relu_with_minmax_equals_minimax_of_its_output(actnn, dtype, shape):
+    from actnn_b200.cpp_extension import minimax, quantization as q
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(shape, generator=g).to(dtype).cuda()
+    x.view(-1)[3] = float("nan")                                   # decodes to 0 like every non-positive input
+    y0, mask0 = q.relu_forward(x)
+    y, mask, mn, mx = q.relu_forward(x, with_minmax=True)
+    assert torch.equal(y, y0) and torch.equal(mask, mask0)
+    rmn, rmx = minimax.minimax(y.view(-1, 256))
+    assert torch.equal(mn, rmn.view(-1)) and torch.equal(mx, rmx.view(-1))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_conv_after_relu_compresses_the_same_with_and_without_the_relu_ranges(actnn, dtype):
+    """QReLU -> QConv2d at level L3: with ``config.relu_minmax`` the convolution takes the ranges
+    from the ReLU pass (one read of its input instead of two); what it saves, what it returns and
+    what it computes must be bit-identical to the two-read path."""
+    actnn.set_optimization_level("L3")
+    torch.manual_seed(0)
+    relu, first = actnn.QReLU(), actnn.QConv2d(16, 8, 3, padding=1).cuda().to(dtype)
+    weights = first.state_dict()
+    x0 = torch.randn(6, 16, 16, 16, device="cuda", dtype=dtype)
+    gy = torch.randn(6, 8, 16, 16, device="cuda", dtype=dtype)
+    gen = torch.cuda.default_generators[torch.cuda.current_device()]
+    results = []
+    for flag in (True, False):
+        actnn.config.relu_minmax = flag
+        actnn.QScheme.layers.clear()                             # a fresh layer: the per-layer widths adapt after a step
+        conv = actnn.QConv2d(16, 8, 3, padding=1).cuda().to(dtype)
+        conv.load_state_dict(weights)
+        conv.scheme.scales = torch.tensor(0.37)
+        gen.manual_seed(123)
+        x = x0.clone().requires_grad_(True)
+        h = relu(x)
+        assert hasattr(h, "actnn_minmax") == flag
+        saved = {}
+        from actnn_b200 import ops
+        real = ops.quantize_activation
+
+        def spy(inp, scheme, minmax=None):
+            out = real(inp, scheme, minmax=minmax)
+            saved["minmax_used"] = minmax is not None
+            saved["q"] = [t.clone() if isinstance(t, torch.Tensor) else t for t in out]
+            return out
+
+        ops.quantize_activation = spy
+        try:
+            y = conv(h)
+        finally:
+            ops.quantize_activation = real
+        assert saved["minmax_used"] == flag
+        y.backward(gy)
+        results.append((y.detach(), x.grad, conv.weight.grad, *saved["q"]))
+    for i, (a, b) in enumerate(zip(*results)):
+        if i in (1, 2):            # gradients come from cuDNN, whose algorithm choice may differ between two calls
+            assert torch.allclose(a.float(), b.float(), rtol=1e-4, atol=1e-5)
+        else:
+            assert torch.equal(a, b)
