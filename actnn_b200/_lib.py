@@ -111,6 +111,20 @@ def scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     return buf
 
 
+_tickets = {}
+
+
+def ticket(device: torch.device) -> torch.Tensor:
+    """256 zeroed bytes per (device, current stream) that only ``actnn_compress_mixed_prestat_kept``
+    uses: its kernels leave the ticket at zero, so it never needs clearing again."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, stream_of_index(idx))
+    buf = _tickets.get(key)
+    if buf is None:
+        buf = _tickets[key] = torch.zeros(256, dtype=torch.uint8, device=device)
+    return buf
+
+
 _fns = {}
 _fast = None
 FAST_PATH = os.path.join(_HERE, "csrc", "_actnn_fastcall.so")

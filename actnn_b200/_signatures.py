@@ -20,6 +20,8 @@ SIGNATURES = {
                                     'U', 'P'],
     "actnn_compress_mixed_prestat": ['P', 'P', 'P', 'P', 'P', 'P', 'P', 'P', 'P', 'P', 'L', 'L', 'L', 'I', 'I', 'F', 'F', 'P', 'I', 'D', 'I',
                                      'P', 'U', 'U', 'P'],
+    "actnn_compress_mixed_prestat_kept": ['P'] * 10 + ['L', 'L', 'L', 'I', 'I', 'F', 'F', 'P', 'I', 'D', 'I', 'P', 'U', 'U',
+                                          'P'],
     "actnn_batch_norm_stats_minimax": ['P'] * 9 + ['L', 'L', 'L', 'D', 'D', 'I', 'P', 'L', 'P'],
     "actnn_range_sqr": ['P', 'P', 'L', 'L', 'I', 'F', 'F', 'P', 'P', 'P'],
     "actnn_sample_sumsq": ['P', 'P', 'L', 'L', 'I', 'P'],

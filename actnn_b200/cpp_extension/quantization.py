@@ -134,8 +134,8 @@ def compress_mixed_precision(data, target_bits: int, initial_bits: int, range_fa
         check_cuda_tensor(gmx, "max", dtype=data.dtype)
         if gmn.numel() != n * g or gmx.numel() != n * g:
             raise RuntimeError("min / max must have one element per group!")
-        workspace = _lib.scratch(dev, 256)
-        _lib.call("actnn_compress_mixed_prestat", data, data.data_ptr(), gmn.data_ptr(), gmx.data_ptr(),
+        workspace = _lib.ticket(dev)
+        _lib.call("actnn_compress_mixed_prestat_kept", data, data.data_ptr(), gmn.data_ptr(), gmx.data_ptr(),
                   packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), bits.data_ptr(), offsets.data_ptr(),
                   C.data_ptr(), workspace.data_ptr(), n, g, gs, _lib.dtype_id(data.dtype), _lib.dtype_id(sdt),
                   float(range_factor), float(coeff), _lib.ptr(grad_scale), int(initial_bits), float(target_bits),

@@ -61,13 +61,12 @@ extern "C" int actnn_compress_mixed(const void* data, int32_t* packed, void* sca
 // The same compress when the per-group min / max already exist (actnn_batch_norm_stats_minimax
 // produces them in the pass that computes the batch-norm statistics): sensitivities + greedy
 // allocation, then the pack.  `ticket_workspace`: 256 bytes, 256-byte aligned.
-extern "C" int actnn_compress_mixed_prestat(const void* data, const void* mn, const void* mx, int32_t* packed,
-                                            void* scale, void* mn_out, int32_t* bits_out, int64_t* word_offsets_out,
-                                            float* C_out, void* ticket_workspace, int64_t N, int64_t G,
-                                            int64_t group_size, int dtype, int stat_dtype, float range_factor,
-                                            float coeff, const float* grad_scale, int initial_bits, double target,
-                                            int stochastic, const void* noise, uint64_t seed, uint64_t offset,
-                                            actnn_stream_t stream) {
+static int compress_prestat(const void* data, const void* mn, const void* mx, int32_t* packed, void* scale,
+                            void* mn_out, int32_t* bits_out, int64_t* word_offsets_out, float* C_out,
+                            void* ticket_workspace, int64_t N, int64_t G, int64_t group_size, int dtype,
+                            int stat_dtype, float range_factor, float coeff, const float* grad_scale,
+                            int initial_bits, double target, int stochastic, const void* noise, uint64_t seed,
+                            uint64_t offset, actnn_stream_t stream, bool clear_ticket) {
   if (N < 0 || G < 0 || (group_size != kGroup && !generic_group_ok(group_size))) return ACTNN_ERR_SHAPE;
   if (dtype < ACTNN_F32 || dtype > ACTNN_BF16) return ACTNN_ERR_DTYPE;
   if (initial_bits < 1 || initial_bits > 8) return ACTNN_ERR_BITS;
@@ -79,7 +78,8 @@ extern "C" int actnn_compress_mixed_prestat(const void* data, const void* mn, co
   cudaStream_t s = (cudaStream_t)stream;
   int st;
   if (range_greedy_supported(N, initial_bits)) {
-    if (cudaMemsetAsync(ticket_workspace, 0, sizeof(unsigned), s) != cudaSuccess) return ACTNN_ERR_LAUNCH;
+    if (clear_ticket && cudaMemsetAsync(ticket_workspace, 0, sizeof(unsigned), s) != cudaSuccess)
+      return ACTNN_ERR_LAUNCH;
     st = range_greedy_impl(mn, mx, N, G, dtype, range_factor, coeff, grad_scale, C_out, (unsigned*)ticket_workspace,
                            initial_bits, target, bits_out, word_offsets_out, group_size, s);
     if (st) return st;
@@ -92,6 +92,34 @@ extern "C" int actnn_compress_mixed_prestat(const void* data, const void* mn, co
   }
   return pack_mixed_impl(data, mn, mx, bits_out, word_offsets_out, packed, scale, mn_out, N, G, group_size, dtype,
                          stat_dtype, stochastic, noise, seed, offset, true, s);
+}
+
+extern "C" int actnn_compress_mixed_prestat(const void* data, const void* mn, const void* mx, int32_t* packed,
+                                            void* scale, void* mn_out, int32_t* bits_out, int64_t* word_offsets_out,
+                                            float* C_out, void* ticket_workspace, int64_t N, int64_t G,
+                                            int64_t group_size, int dtype, int stat_dtype, float range_factor,
+                                            float coeff, const float* grad_scale, int initial_bits, double target,
+                                            int stochastic, const void* noise, uint64_t seed, uint64_t offset,
+                                            actnn_stream_t stream) {
+  return compress_prestat(data, mn, mx, packed, scale, mn_out, bits_out, word_offsets_out, C_out, ticket_workspace, N,
+                          G, group_size, dtype, stat_dtype, range_factor, coeff, grad_scale, initial_bits, target,
+                          stochastic, noise, seed, offset, stream, true);
+}
+
+// The same with a ticket word the caller keeps for this purpose only: zero before the first call
+// (one cudaMemset when it is allocated), left at zero by every call (the block that takes the last
+// ticket resets it), never touched by anything else, used by one stream at a time.  Saves the
+// per-call clear: one memory operation less in the stream of every layer.
+extern "C" int actnn_compress_mixed_prestat_kept(const void* data, const void* mn, const void* mx, int32_t* packed,
+                                                 void* scale, void* mn_out, int32_t* bits_out,
+                                                 int64_t* word_offsets_out, float* C_out, void* ticket_workspace,
+                                                 int64_t N, int64_t G, int64_t group_size, int dtype, int stat_dtype,
+                                                 float range_factor, float coeff, const float* grad_scale,
+                                                 int initial_bits, double target, int stochastic, const void* noise,
+                                                 uint64_t seed, uint64_t offset, actnn_stream_t stream) {
+  return compress_prestat(data, mn, mx, packed, scale, mn_out, bits_out, word_offsets_out, C_out, ticket_workspace, N,
+                          G, group_size, dtype, stat_dtype, range_factor, coeff, grad_scale, initial_bits, target,
+                          stochastic, noise, seed, offset, stream, false);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -253,6 +253,16 @@ int actnn_compress_mixed_prestat(const void* data, const void* mn, const void* m
                                  int initial_bits, double target, int stochastic, const void* noise, uint64_t seed,
                                  uint64_t offset, actnn_stream_t stream);
 
+/* actnn_compress_mixed_prestat (same replaced reference code: qbnscheme.py:42-52, quantization.cc:46-57) with a
+ * ticket word that the caller keeps for this purpose only: zero before the first call, left at zero by every
+ * call, touched by nothing else, used by one stream at a time.  The per-call clear of the ticket is skipped. */
+int actnn_compress_mixed_prestat_kept(const void* data, const void* mn, const void* mx, int32_t* packed, void* scale,
+                                      void* mn_out, int32_t* bits_out, int64_t* word_offsets_out, float* C_out,
+                                      void* ticket_workspace, int64_t N, int64_t G, int64_t group_size, int dtype,
+                                      int stat_dtype, float range_factor, float coeff, const float* grad_scale,
+                                      int initial_bits, double target, int stochastic, const void* noise,
+                                      uint64_t seed, uint64_t offset, actnn_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * Mask ops.  The saved mask is 1 bit per element: bit (e % 8) of byte e / 8, padded to
  * whole int32 words (mask_words = ceil(numel / 32)).

@@ -193,3 +193,16 @@ def test_statistics_minmax_pass_stays_inside_its_outputs(env, shape, dtype):
                                                   cm["ticket"].ptr(), n, g, 256, D, S, 1.0, 1.0, None, 8, float(total),
                                                   1, None, 5, 0, st), "actnn_compress_mixed_prestat", cm)
     assert int(cm["bits"].t.sum()) == total
+    # the variant with a kept ticket: same outputs, the ticket is zero before and after, twice in a row
+    first = {k: v.t.clone() for k, v in cm.items() if k != "ticket"}
+    assert int(cm["ticket"].t[:4].view(torch.int32)) == 0               # the call above left it at zero
+    for _ in range(2):
+        _check(_lib, lib.actnn_compress_mixed_prestat_kept(x.data_ptr(), bufs["min"].ptr(), bufs["max"].ptr(),
+                                                           cm["packed"].ptr(), cm["scale"].ptr(), cm["min_out"].ptr(),
+                                                           cm["bits"].ptr(), cm["word_offsets"].ptr(), cm["C"].ptr(),
+                                                           cm["ticket"].ptr(), n, g, 256, D, S, 1.0, 1.0, None, 8,
+                                                           float(total), 1, None, 5, 0, st),
+               "actnn_compress_mixed_prestat_kept", cm)
+        assert int(cm["ticket"].t[:4].view(torch.int32)) == 0
+        for k, v in first.items():
+            assert torch.equal(cm[k].t, v), k
